@@ -1,0 +1,111 @@
+/*
+ * qtip_b200 - C ABI of the B200 (sm_100a) kernels for the QTIP quantized-linear path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the stream it is given
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) on the CURRENT device, does
+ * not synchronise, and returns a status code instead of terminating the process (the upstream
+ * launcher exits on a launch error: qtip-kernels/src/inference.h:10-18).  Unless a comment says
+ * otherwise an entry point allocates nothing, so it may be called while a stream is captured
+ * into a CUDA graph.
+ *
+ * Naming: K = bits per weight (the upstream CUDA template parameter R), m = out_features
+ * (upstream M), n = in_features (upstream template K), bs = batch rows.  fp16 buffers are IEEE
+ * binary16 (uint16_t storage).  "kernel layout" is the packed trellis format written by
+ * lib/algo/finetune.py:196-201 upstream for L=16, V=2, Q=9, 16x16 tiles; "plain layout" is the
+ * output of bitshift_codebook.pack_trellis (lib/codebook/bitshift.py:294-327).
+ */
+#ifndef QTIP_B200_H
+#define QTIP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    QTIP_OK = 0,
+    QTIP_ERR_BAD_ARG = 1,      /* NULL pointer, unsupported K / code / dtype, bs out of range */
+    QTIP_ERR_BAD_SHAPE = 2,    /* m or n not a multiple of the tile block, size has no Hadamard factorisation */
+    QTIP_ERR_WORKSPACE = 3,    /* workspace missing or too small */
+    QTIP_ERR_CUDA = 4,         /* a CUDA runtime call or the launch failed; see qtip_last_cuda_error() */
+    QTIP_ERR_ALIGNMENT = 5     /* a pointer is not aligned as documented */
+};
+
+enum { QTIP_CODE_HYB = 0, QTIP_CODE_3INST = 1, QTIP_CODE_1MAD = 2 };
+enum { QTIP_F16 = 0, QTIP_F32 = 1 };
+
+/* Human-readable text for a status code; never NULL. */
+const char *qtip_status_string(int status);
+/* cudaError_t (as int) recorded by the last failing call on this host thread, 0 if none. */
+int qtip_last_cuda_error(void);
+/* Library version, major*100 + minor. */
+int qtip_version(void);
+
+/* --------------------------------------------------------------------------------------------
+ * Decoders (trellis codes -> dense fp16 matrix W, row-major (m, n), y = x @ W^T).
+ * ------------------------------------------------------------------------------------------ */
+
+/* HYB code, kernel layout.  Replaces decode_compressed (lib/utils/kernel_decompress.py:4-55) and
+ * BitshiftLinear.get_hatW_kernel (lib/codebook/bitshift.py:383-387); bit-exact with them.
+ * codes: K*m*n/8 bytes, 16-byte aligned; tlut: 512x2 fp16; m, n multiples of 32; K in {2,3,4}. */
+int qtip_decode_hyb(void *W, const void *codes, const void *tlut, int K, int m, int n, void *stream);
+
+/* Plain layout, any of the three codes.  Replaces unpack_trellis + recons + get_hatW
+ * (lib/codebook/bitshift.py:329-353, 199-201, 378-381).  HYB uses V=2 and needs tlut; 3INST and
+ * 1MAD use V=1, ignore tlut, and are the state functions decode_3inst / decode_1mad (:43-60,
+ * :17-26); 1MAD's fp32 value is rounded once (nearest-even) to fp16.  m, n multiples of 16. */
+int qtip_decode_plain(void *W, const void *codes, int code, const void *tlut, int K, int m, int n, void *stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Fused decode + matvec:  out[b][r] = sum_c W[r][c] * x[b][c],  fp16 operands, fp32 accumulate.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Bytes of workspace qtip_decompress_matvec / _plain need for this problem (never 0). */
+size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
+
+/* HYB code, kernel layout.  Replaces the 64 fixed-shape functions
+ * decompress_matvec_16_9_{K}_1_{m}_1_{n}(out, compressed, x, codebook)
+ * (qtip-kernels/src/qtip_torch.cu:14-57 and :60-671, kernel qtip-kernels/src/inference.cu:168-425)
+ * with one shape-generic call, and extends them to bs <= 8 rows of x.
+ * out: (bs, m) fp32, OVERWRITTEN (need not be zeroed); x: (bs, n) fp16, 4-byte aligned rows;
+ * codes 16-byte aligned; tlut 512x2 fp16.  m, n multiples of 32.
+ * workspace: qtip_matvec_workspace_bytes() bytes, 256-byte aligned, ZEROED ONCE by the caller
+ * before its first use (the kernel leaves it zeroed again); calls that may overlap on the device
+ * need separate workspaces. */
+int qtip_decompress_matvec(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
+                           int bs, void *workspace, size_t workspace_bytes, void *stream);
+
+/* 3INST / 1MAD, plain layout, V=1; same contract as above (no LUT).  The decoded weights are the
+ * ones qtip_decode_plain produces.  m, n multiples of 32. */
+int qtip_decompress_matvec_plain(float *out, const void *codes, const void *x, int code, int K, int m, int n,
+                                 int bs, void *workspace, size_t workspace_bytes, void *stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Randomized Hadamard transform.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out[r][:] = sign_out ⊙ ( H_n ( sign_in ⊙ in[r][:] ) ) * scale      for each of `rows` rows.
+ * H_n is the UNNORMALISED transform of matmul_hadU_cuda (lib/utils/matmul_had.py:105-119):
+ * n = kfac * 2^p viewed (kfac, n/kfac), Walsh-Hadamard over the last dim, then hadK (kfac x kfac)
+ * from the left - hadK^T when `transpose` is non-zero (matmul_hadUt_cuda, :118-119).  The caller
+ * folds n^-1/2 and the /32, x32 factors of BitshiftLinear.forward (lib/codebook/bitshift.py:428-441,
+ * 465-471) into `scale` and sign_out.  Replaces the hadamard::hadamard op (third-party
+ * fast_hadamard_transform) plus the element-wise kernels around it.
+ *   in / out      : (rows, n), dtype QTIP_F16 or QTIP_F32 each; may alias only if identical.
+ *   sign_in       : NULL or n_signs values of dtype sign_in_dtype; sign_out: NULL or n_signs fp32.
+ *   n_signs       : n, or a multiple t*n - then row r uses signs [(r % t)*n, (r % t + 1)*n)
+ *                   (the per-chunk transforms of the tensor-parallel layouts, :437-441, :465-469).
+ *   hadk_bits     : NULL when kfac == 1, else kfac rows of ceil(kfac/32) uint32 words, bit j of
+ *                   word w of row i set when hadK[i][32w+j] == +1.
+ *   kfac in {1,12,20,28,36,52,60,108,116,124,140,156,172}; n/kfac a power of two, 2 <= n/kfac,
+ *   n <= 65536. */
+int qtip_rht(void *out, int out_dtype, const void *in, int in_dtype, long rows, int n, const void *sign_in,
+             int sign_in_dtype, const float *sign_out, long n_signs, const uint32_t *hadk_bits, int kfac,
+             int transpose, float scale, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QTIP_B200_H */

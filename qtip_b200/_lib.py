@@ -1,0 +1,54 @@
+"""ctypes binding of libqtip_b200.so (the C ABI declared in include/qtip_b200.h).
+
+There is no fallback: if the shared library is missing or a call returns a non-zero status a
+RuntimeError is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libqtip_b200.so")
+
+OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_WORKSPACE, ERR_CUDA, ERR_ALIGNMENT = range(6)
+CODE_HYB, CODE_3INST, CODE_1MAD = 0, 1, 2
+F16, F32 = 0, 1
+
+_vp, _i, _l, _sz, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t, ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/qtip_b200.h
+SIGNATURES = {
+    "qtip_status_string": (ctypes.c_char_p, [_i]),
+    "qtip_last_cuda_error": (_i, []),
+    "qtip_version": (_i, []),
+    "qtip_decode_hyb": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "qtip_decode_plain": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "qtip_matvec_workspace_bytes": (_sz, [_i, _i, _i]),
+    "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the library (once).  Raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise RuntimeError(f"{SO_PATH} is missing: build it with `python -m qtip_b200.build` "
+                               "(qtip_b200 has no fallback path)")
+        lib = ctypes.CDLL(SO_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status, what):
+    if status != OK:
+        lib = load()
+        msg = lib.qtip_status_string(status).decode()
+        extra = f" (cudaError {lib.qtip_last_cuda_error()})" if status == ERR_CUDA else ""
+        raise RuntimeError(f"{what}: {msg}{extra}")

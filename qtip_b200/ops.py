@@ -1,0 +1,224 @@
+"""Tensor-level wrappers over the C ABI (include/qtip_b200.h).
+
+All functions run on the tensors' CUDA device and the current torch stream, never synchronise,
+and raise RuntimeError on any non-zero status.  There is no CPU path.
+"""
+import math
+import os
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import CODE_1MAD, CODE_3INST, CODE_HYB, F16, F32  # noqa: F401
+
+CODE_IDS = {"quantlut_sym": CODE_HYB, "hyb": CODE_HYB, "3inst": CODE_3INST, "1mad": CODE_1MAD}
+HAD_FACTORS = (172, 156, 140, 124, 116, 108, 60, 52, 36, 28, 20, 12)
+MAX_MATVEC_BATCH = 8
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("qtip_b200 runs on CUDA tensors only (no CPU fallback)")
+
+
+def _dtype_id(t):
+    if t.dtype == torch.float16:
+        return F16
+    if t.dtype == torch.float32:
+        return F32
+    raise RuntimeError(f"unsupported dtype {t.dtype} (fp16 / fp32 only)")
+
+
+# ---------------------------------------------------------------------------------------------
+# Hadamard factor matrices
+# ---------------------------------------------------------------------------------------------
+_HADK_NPZ = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "hadk.npz")
+_hadk_cpu = {}
+_hadk_bits_dev = {}
+
+
+def had_factor(n):
+    """Factor order K of n = K * 2^p, first match in the order of get_hadK upstream
+    (lib/utils/matmul_had.py:9-63); 1 for a power of two."""
+    for k in HAD_FACTORS:
+        if n % k == 0:
+            q = n // k
+            if q & (q - 1) != 0:
+                raise ValueError(f"{n} / {k} is not a power of two")
+            return k
+    if n <= 0 or n & (n - 1):
+        raise ValueError(f"{n} has no supported Hadamard factorisation")
+    return 1
+
+
+def get_hadK(n, transpose=False):
+    """(hadK fp32 (K, K) or None, K) for a width n - the contract of get_hadK upstream."""
+    k = had_factor(n)
+    if k == 1:
+        return None, 1
+    if k not in _hadk_cpu:
+        with np.load(_HADK_NPZ) as z:
+            bits = np.unpackbits(z[f"had{k}"])[:k * k].reshape(k, k)
+        _hadk_cpu[k] = torch.from_numpy(bits.astype(np.float32) * 2 - 1)
+    h = _hadk_cpu[k]
+    return (h.T.contiguous() if transpose else h.clone()), k
+
+
+def pack_hadk(hadK):
+    """+-1 matrix (K, K) -> int32 tensor (K, ceil(K/32)) of sign bits for qtip_rht, on hadK's device."""
+    k = hadK.shape[0]
+    wpr = (k + 31) // 32
+    bits = (hadK > 0).to(torch.int64)
+    pad = torch.zeros(k, wpr * 32, dtype=torch.int64, device=hadK.device)
+    pad[:, :k] = bits
+    w = (pad.view(k, wpr, 32) << torch.arange(32, device=hadK.device, dtype=torch.int64)).sum(-1)
+    w = torch.where(w >= 2**31, w - 2**32, w)
+    return w.to(torch.int32).contiguous()
+
+
+def hadk_bits_for(hadK, device):
+    """Device-resident packed signs of a factor matrix, cached by (order, device, content hash)."""
+    if hadK is None:
+        return None
+    k = hadK.shape[0]
+    key = (k, str(device), hadK.data_ptr(), hadK._version)
+    hit = _hadk_bits_dev.get(key)
+    if hit is None:
+        hit = pack_hadk(hadK.detach().to(device=device, dtype=torch.float32))
+        _hadk_bits_dev[key] = hit
+    return hit
+
+
+# ---------------------------------------------------------------------------------------------
+# workspace for the fused matvec (ticket counters + partial sums), zeroed once at allocation
+# ---------------------------------------------------------------------------------------------
+_workspaces = {}
+
+
+def matvec_workspace(m, n, bs, device):
+    """A zero-initialised workspace tensor private to (device, current stream)."""
+    need = _lib.load().qtip_matvec_workspace_bytes(m, n, bs)
+    key = (torch.device(device).index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+# ---------------------------------------------------------------------------------------------
+# ops
+# ---------------------------------------------------------------------------------------------
+def decode_hyb(codes, tlut, K, m, n, out=None):
+    """Kernel-layout HYB codes -> (m, n) fp16 (decode_compressed upstream)."""
+    _require_cuda(codes, tlut)
+    codes = codes.contiguous()
+    tlut = tlut.to(torch.float16).contiguous()
+    if codes.numel() * codes.element_size() != m * n * K // 8:
+        raise RuntimeError(f"codes hold {codes.numel() * codes.element_size()} bytes, expected {m * n * K // 8}")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float16, device=codes.device)
+    with torch.cuda.device(codes.device):
+        st = _lib.load().qtip_decode_hyb(out.data_ptr(), codes.data_ptr(), tlut.data_ptr(), K, m, n, _stream())
+    _lib.check(st, "qtip_decode_hyb")
+    return out
+
+
+def decode_plain(codes, code, K, m, n, tlut=None, out=None):
+    """Plain-layout codes of any of the three codes -> (m, n) fp16 (unpack_trellis + get_hatW upstream)."""
+    _require_cuda(codes, tlut)
+    code = CODE_IDS.get(code, code)
+    codes = codes.contiguous()
+    if codes.numel() * codes.element_size() != m * n * K // 8:
+        raise RuntimeError(f"codes hold {codes.numel() * codes.element_size()} bytes, expected {m * n * K // 8}")
+    tl = None if tlut is None else tlut.to(torch.float16).contiguous()
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float16, device=codes.device)
+    with torch.cuda.device(codes.device):
+        st = _lib.load().qtip_decode_plain(out.data_ptr(), codes.data_ptr(), code, None if tl is None else tl.data_ptr(),
+                                           K, m, n, _stream())
+    _lib.check(st, "qtip_decode_plain")
+    return out
+
+
+def decompress_matvec(codes, x, tlut, K, m, n, out=None, workspace=None):
+    """out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T, HYB kernel layout, bs <= 8."""
+    _require_cuda(codes, x, tlut)
+    if x.dtype != torch.float16:
+        x = x.to(torch.float16)
+    x = x.reshape(-1, n).contiguous()
+    bs = x.shape[0]
+    if out is None:
+        out = torch.empty(bs, m, dtype=torch.float32, device=x.device)
+    if workspace is None:
+        workspace = matvec_workspace(m, n, bs, x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().qtip_decompress_matvec(out.data_ptr(), codes.data_ptr(), x.data_ptr(), tlut.data_ptr(), K, m,
+                                                n, bs, workspace.data_ptr(), workspace.numel(), _stream())
+    _lib.check(st, "qtip_decompress_matvec")
+    return out
+
+
+def decompress_matvec_plain(codes, x, code, K, m, n, out=None, workspace=None):
+    """Same for the 3INST / 1MAD compute codes (plain layout, V = 1)."""
+    _require_cuda(codes, x)
+    code = CODE_IDS.get(code, code)
+    if x.dtype != torch.float16:
+        x = x.to(torch.float16)
+    x = x.reshape(-1, n).contiguous()
+    bs = x.shape[0]
+    if out is None:
+        out = torch.empty(bs, m, dtype=torch.float32, device=x.device)
+    if workspace is None:
+        workspace = matvec_workspace(m, n, bs, x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().qtip_decompress_matvec_plain(out.data_ptr(), codes.data_ptr(), x.data_ptr(), code, K, m, n, bs,
+                                                      workspace.data_ptr(), workspace.numel(), _stream())
+    _lib.check(st, "qtip_decompress_matvec_plain")
+    return out
+
+
+def rht(x, sign_in=None, sign_out=None, hadk_bits=None, kfac=1, transpose=False, scale=1.0, out_dtype=None, out=None):
+    """out = sign_out * H(sign_in * x) * scale over the last dim of x (rows, n); see qtip_rht."""
+    _require_cuda(x, sign_in, sign_out, hadk_bits)
+    n = x.shape[-1]
+    x2 = x.reshape(-1, n)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    if out_dtype is None:
+        out_dtype = x.dtype
+    if out is None:
+        out = torch.empty(rows, n, dtype=out_dtype, device=x.device)
+    n_signs = n
+    if sign_in is not None:
+        sign_in = sign_in.contiguous()
+        n_signs = sign_in.numel()
+    if sign_out is not None:
+        sign_out = sign_out.to(torch.float32).contiguous()
+        if sign_in is not None and sign_out.numel() != n_signs:
+            raise RuntimeError("sign_in and sign_out must have the same length")
+        n_signs = sign_out.numel()
+    with torch.cuda.device(x.device):
+        st = _lib.load().qtip_rht(out.data_ptr(), _dtype_id(out), x2.data_ptr(), _dtype_id(x2), rows, n,
+                                  None if sign_in is None else sign_in.data_ptr(),
+                                  F16 if sign_in is None else _dtype_id(sign_in),
+                                  None if sign_out is None else sign_out.data_ptr(), n_signs,
+                                  None if hadk_bits is None else hadk_bits.data_ptr(), kfac, int(bool(transpose)),
+                                  float(scale), _stream())
+    _lib.check(st, "qtip_rht")
+    return out.reshape(*x.shape[:-1], n)
+
+
+def hadamard(x, hadK=None, K=1, transpose=False):
+    """Orthonormal Hadamard over the last dim: drop-in for matmul_hadU_cuda / matmul_hadUt_cuda
+    (lib/utils/matmul_had.py:105-119 upstream)."""
+    n = x.shape[-1]
+    bits = hadk_bits_for(hadK, x.device) if K > 1 else None
+    return rht(x, hadk_bits=bits, kfac=K, transpose=transpose, scale=1.0 / math.sqrt(n))

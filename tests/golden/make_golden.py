@@ -75,7 +75,7 @@ def main():
     # ---- full layer -------------------------------------------------------------------------------
     out = {"tlut": tlut.numpy()}
     cases = [("hyb", 2, 256, 512, 0, 1), ("hyb", 2, 256, 512, 1, 1), ("hyb", 2, 256, 512, 2, 1),
-             ("hyb", 3, 688, 256, 0, 1), ("hyb", 4, 256, 832, 0, 2),
+             ("hyb", 3, 688, 256, 0, 1), ("hyb", 3, 1376, 256, 0, 1), ("hyb", 4, 256, 832, 0, 2),
              ("3inst", 2, 128, 256, 0, 1), ("1mad", 2, 128, 256, 0, 3)]
     for (mode, K, m, n, rcp, bs) in cases:
         V = 2 if mode == "hyb" else 1

@@ -1,0 +1,77 @@
+"""CPU: the C-ABI library loads, exports every symbol the header declares, and validates arguments
+before touching the device (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from qtip_b200 import _lib
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "qtip_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qtip_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    names = declared_functions()
+    assert names, "no declarations found"
+    assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
+
+
+def test_every_declared_symbol_is_exported():
+    lib = ctypes.CDLL(_lib.SO_PATH)
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} declared in include/qtip_b200.h but not exported"
+
+
+def test_status_strings():
+    lib = _lib.load()
+    assert lib.qtip_status_string(0) == b"ok"
+    for s in range(1, 6):
+        assert lib.qtip_status_string(s) not in (b"ok", b"unknown status")
+    assert lib.qtip_status_string(99) == b"unknown status"
+    assert lib.qtip_version() >= 1
+
+
+def test_argument_validation_without_device():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p = (p + 255) & ~255
+    assert lib.qtip_decode_hyb(None, p, p, 2, 32, 32, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_decode_hyb(p, p, p, 5, 32, 32, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_decode_hyb(p, p, p, 2, 48, 32, None) == _lib.ERR_BAD_SHAPE
+    assert lib.qtip_decode_hyb(p, p + 4, p, 2, 32, 32, None) == _lib.ERR_ALIGNMENT
+    assert lib.qtip_decode_plain(p, p, 7, p, 2, 32, 32, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_decode_plain(p, p, _lib.CODE_HYB, None, 2, 32, 32, None) == _lib.ERR_BAD_ARG
+    need = lib.qtip_matvec_workspace_bytes(64, 64, 1)
+    assert need >= 256
+    assert lib.qtip_decompress_matvec(p, p, p, p, 2, 64, 64, 9, p, need, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_decompress_matvec(p, p, p, p, 2, 64, 64, 1, None, 0, None) == _lib.ERR_WORKSPACE
+    assert lib.qtip_decompress_matvec(p, p, p, p, 2, 64, 64, 1, p, need - 1, None) == _lib.ERR_WORKSPACE
+    assert lib.qtip_decompress_matvec(p, p, p, p, 2, 64, 40, 1, p, need, None) == _lib.ERR_BAD_SHAPE
+    assert lib.qtip_decompress_matvec_plain(p, p, p, _lib.CODE_HYB, 2, 64, 64, 1, p, need, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_rht(p, 0, p, 0, 1, 24, None, 0, None, 24, None, 1, 0, 1.0, None) == _lib.ERR_BAD_SHAPE
+    assert lib.qtip_rht(p, 0, p, 0, 1, 344, None, 0, None, 344, None, 172, 0, 1.0, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_rht(p, 3, p, 0, 1, 64, None, 0, None, 64, None, 1, 0, 1.0, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_rht(p, 0, p, 0, 0, 64, None, 0, None, 64, None, 1, 0, 1.0, None) == _lib.OK  # zero rows: nothing to do
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "SO_PATH", os.path.join(ROOT, "does_not_exist.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from qtip_b200 import ops
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.decode_hyb(torch.zeros(32 * 32 * 2 // 16, dtype=torch.int16), torch.zeros(512, 2, dtype=torch.float16), 2, 32, 32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.rht(torch.zeros(1, 64))

@@ -1,0 +1,179 @@
+"""GPU parity: every CUDA entry point, called through the C ABI, against the CPU oracles.
+
+Decoders must be bit-exact (uint16 views, including -0.0).  The fused matvec and the layer forward
+must agree with the oracle within relative L2 1e-3 (the fp16 budget of the path); the transforms,
+being fp32, within 1e-5.
+"""
+import numpy as np
+import pytest
+import torch
+
+import c_oracle as C
+import qtip_oracle as O
+from conftest import rel_l2
+from qtip_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a):
+    if a.dtype == np.uint16:
+        return torch.from_numpy(a.view(np.int16)).to(DEV)
+    return torch.from_numpy(a).to(DEV)
+
+
+def u16(t):
+    if torch.is_tensor(t):
+        t = t.cpu().numpy()
+    return np.ascontiguousarray(t).view(np.uint16)
+
+
+# ---- decoders: bit exact ---------------------------------------------------------------------------
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("shape", ["32x64", "64x96"])
+def test_decode_hyb_golden(golden, K, shape):
+    g = golden("decode_kernel")
+    m, n = map(int, shape.split("x"))
+    W = ops.decode_hyb(dev(g[f"codes_K{K}_{shape}"]), dev(g["tlut"]), K, m, n)
+    assert np.array_equal(u16(W), u16(g[f"W_K{K}_{shape}"]))
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("m,n", [(256, 256), (4096, 4096), (4096, 11008), (11008, 4096)])
+def test_decode_hyb_vs_oracle(K, m, n):
+    lay = synth.make_layer(m, n, K, seed=2000 + K)
+    W = ops.decode_hyb(dev(lay["codes"]), dev(lay["tlut"]), K, m, n)
+    assert np.array_equal(u16(W), u16(C.decode_kernel(lay["codes"], m, n, K, lay["tlut"])))
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("mode", ["3inst", "1mad", "quantlut_sym"])
+def test_decode_plain_golden(golden, K, mode):
+    g = golden("decode_plain")
+    W = ops.decode_plain(dev(g[f"codes_{mode}_K{K}"]), mode, K, 32, 64, tlut=dev(g["tlut"]))
+    # 3INST values are fp16-exact; 1MAD is upstream's fp32 value rounded once to fp16
+    assert np.array_equal(u16(W), u16(g[f"W_{mode}_K{K}"].astype(np.float16)))
+
+
+@pytest.mark.parametrize("code,V", [(O.CODE_3INST, 1), (O.CODE_1MAD, 1), (O.CODE_HYB, 2)])
+@pytest.mark.parametrize("K,m,n", [(2, 64, 96), (3, 256, 256), (4, 64, 96), (2, 8192, 8192)])
+def test_decode_plain_vs_oracle(code, V, K, m, n):
+    lay = synth.make_layer(m, n, K, seed=2100 + K)
+    W = ops.decode_plain(dev(lay["codes"]), code, K, m, n, tlut=dev(lay["tlut"]))
+    want = C.decode_plain(lay["codes"], m, n, K, V, O.state_table(code, lay["tlut"]))
+    assert np.array_equal(u16(W), u16(want))
+
+
+def test_state_functions_all_65536_states():
+    """Every state value through both compute codes and the HYB hash: a stream whose windows enumerate
+    all 16-bit states (K=4, V=1 / V=2 tiles filled with a counter pattern would not cover them), so
+    instead decode random tiles until every state was seen at least once."""
+    K, m, n = 4, 512, 512
+    lay = synth.make_layer(m, n, K, seed=5)
+    st = O.states_plain_layout(lay["codes"], m, n, K, 1)
+    assert np.unique(st).size > 64000
+    for code in (O.CODE_3INST, O.CODE_1MAD):
+        W = ops.decode_plain(dev(lay["codes"]), code, K, m, n)
+        assert np.array_equal(u16(W), u16(O.decode_plain_layout(lay["codes"], m, n, K, 1, code)))
+
+
+# ---- fused matvec ----------------------------------------------------------------------------------
+def test_known_answer():
+    """qtip-kernels/src/test.cu:22-58 upstream: zero codes, LUT 1.0, x 1.0 => every output is exactly n."""
+    for (m, n) in ((8192, 8192), (64, 256)):
+        codes = torch.zeros(m * n // 256, 32, dtype=torch.int16, device=DEV)
+        tlut = torch.ones(512, 2, dtype=torch.float16, device=DEV)
+        x = torch.ones(1, n, dtype=torch.float16, device=DEV)
+        y = ops.decompress_matvec(codes, x, tlut, 2, m, n)
+        assert torch.all(y == n)
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("m,n,bs", [(32, 64, 1), (64, 96, 1), (256, 256, 1), (4096, 4096, 1), (4096, 11008, 1),
+                                    (11008, 4096, 1), (1024, 8192, 1), (4096, 4096, 4), (512, 1024, 8)])
+def test_matvec_hyb(K, m, n, bs):
+    lay = synth.make_layer(m, n, K, seed=3000 + K, bs=bs)
+    out = torch.full((bs, m), float("nan"), device=DEV)  # the op overwrites, it must not accumulate
+    y = ops.decompress_matvec(dev(lay["codes"]), dev(lay["x"]), dev(lay["tlut"]), K, m, n, out=out)
+    want = C.matvec_kernel(lay["codes"], m, n, K, lay["tlut"], lay["x"])
+    assert rel_l2(y.cpu().numpy(), want) < 1e-3
+    assert rel_l2(y.cpu().numpy(), want) < 2e-6  # fp32 accumulation of exact fp16 products: only summation order differs
+    y2 = ops.decompress_matvec(dev(lay["codes"]), dev(lay["x"]), dev(lay["tlut"]), K, m, n)
+    assert torch.equal(y, y2), "result must be deterministic run to run"
+
+
+def test_matvec_hyb_upstream_test_inputs():
+    """Inputs shaped like prepare_arguments of qtip-kernels/test_decompress_matvec.py:251-272 upstream
+    (codebook and x ~ N(0,1)/16 clamped to [-1,1]); acceptance as there: allclose(atol=1e-5, rtol=1e-2) in fp16."""
+    g = torch.Generator().manual_seed(42)
+    for K in (2, 3, 4):
+        for (m, n) in ((256, 256), (8192, 1024), (1024, 8192)):
+            cb = (torch.randn(1024, generator=g).half() / 16).clamp(-1, 1)
+            codes = torch.randint(-2**31, 2**31, (K * m * n // 32,), generator=g, dtype=torch.int64).to(torch.int32)
+            x = (torch.randn(n, 1, generator=g).half() / 16).clamp(-1, 1)
+            y = ops.decompress_matvec(codes.to(DEV), x.to(DEV).view(1, n), cb.to(DEV), K, m, n)
+            W = C.decode_kernel(codes.numpy(), m, n, K, cb.numpy())
+            ref = torch.from_numpy(C.matvec_dense(W, x.numpy().reshape(1, n)))
+            assert torch.allclose(y.cpu().half(), ref.half(), atol=1e-5, rtol=0.01)
+
+
+@pytest.mark.parametrize("code", [O.CODE_3INST, O.CODE_1MAD])
+@pytest.mark.parametrize("K,m,n,bs", [(2, 32, 64, 1), (2, 256, 256, 1), (3, 64, 96, 2), (4, 128, 256, 8),
+                                      (2, 8192, 8192, 1), (2, 8192, 8192, 4)])
+def test_matvec_plain(code, K, m, n, bs):
+    lay = synth.make_layer(m, n, K, seed=3100 + K, bs=bs, code="none")
+    y = ops.decompress_matvec_plain(dev(lay["codes"]), dev(lay["x"]), code, K, m, n)
+    W = C.decode_plain(lay["codes"], m, n, K, 1, O.state_table(code))
+    want = C.matvec_dense(W, lay["x"])
+    assert rel_l2(y.cpu().numpy(), want) < 1e-3
+    assert rel_l2(y.cpu().numpy(), want) < 2e-6
+
+
+# ---- Hadamard -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [128, 896, 2048, 4096, 6656, 11008])
+def test_hadamard_golden(golden, n):
+    g = golden("hadamard")
+    hk, k = ops.get_hadK(n)
+    x = dev(g[f"x_{n}"])
+    hk = None if hk is None else hk.to(DEV)
+    assert rel_l2(ops.hadamard(x, hk, k).cpu().numpy(), g[f"y_{n}"]) < 1e-5
+    assert rel_l2(ops.hadamard(x, hk, k, transpose=True).cpu().numpy(), g[f"yt_{n}"]) < 1e-5
+
+
+@pytest.mark.parametrize("n", [2, 64, 8192, 14336, 16384, 28672, 53248])
+def test_rht_vs_oracle(n):
+    rng = np.random.default_rng(n)
+    rows = 3
+    x = rng.standard_normal((rows, n)).astype(np.float32)
+    su = np.sign(rng.standard_normal(n)).astype(np.float16)
+    sv = (np.sign(rng.standard_normal(n)) * (0.5 + rng.random(n))).astype(np.float32)
+    hk, k = ops.get_hadK(n)
+    bits = None if hk is None else ops.pack_hadk(hk.to(DEV))
+    hkn = None if hk is None else hk.numpy()
+    # input side: fp32 in, fp16 out, sign in, transposed factor
+    got = ops.rht(dev(x), sign_in=dev(su), hadk_bits=bits, kfac=k, transpose=True, scale=1 / np.sqrt(n) / 32,
+                  out_dtype=torch.float16)
+    want = O.hadamard(x * su.astype(np.float32), hkn, transpose=True) / 32
+    assert rel_l2(got.float().cpu().numpy(), want) < 6e-4  # fp16 output rounding
+    # output side: fp32 in, fp32 out, sign out
+    got = ops.rht(dev(x), sign_out=dev(sv), hadk_bits=bits, kfac=k, scale=1 / np.sqrt(n))
+    want = O.hadamard(x, hkn) * sv
+    assert rel_l2(got.cpu().numpy(), want) < 1e-5
+    # fp16 in
+    xh = x.astype(np.float16)
+    got = ops.rht(dev(xh), hadk_bits=bits, kfac=k, scale=1 / np.sqrt(n), out_dtype=torch.float32)
+    assert rel_l2(got.cpu().numpy(), O.hadamard(xh.astype(np.float32), hkn)) < 1e-5
+
+
+def test_rht_chunked_signs():
+    """Per-chunk transforms of the tensor-parallel layouts: rows cycle through the chunks of the sign vector."""
+    rng = np.random.default_rng(0)
+    bs, tp, seg = 2, 8, 832  # 832 = 52 * 16
+    x = rng.standard_normal((bs, tp * seg)).astype(np.float32)
+    su = np.sign(rng.standard_normal(tp * seg)).astype(np.float32)
+    hk, k = ops.get_hadK(seg)
+    got = ops.rht(dev(x).reshape(bs * tp, seg), sign_in=dev(su), hadk_bits=ops.pack_hadk(hk.to(DEV)), kfac=k,
+                  transpose=True, scale=1 / np.sqrt(seg)).reshape(bs, tp * seg)
+    want = O.hadamard((x * su).reshape(bs * tp, seg), hk.numpy(), transpose=True).reshape(bs, tp * seg)
+    assert rel_l2(got.cpu().numpy(), want) < 1e-5

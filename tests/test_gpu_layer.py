@@ -1,0 +1,146 @@
+"""GPU parity of the module-level interfaces: BitshiftLinear.forward, QuantizedLinear, the qtip_kernels shim."""
+import numpy as np
+import pytest
+import torch
+
+import c_oracle as C
+import qtip_oracle as O
+from conftest import rel_l2
+from qtip_b200 import ops, qtip_kernels, synth
+from qtip_b200.bitshift import BitshiftLinear
+from qtip_b200.quantized_linear import QuantizedLinear
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+LAYER_CASES = [("hyb", 2, 256, 512, 0), ("hyb", 2, 256, 512, 1), ("hyb", 2, 256, 512, 2), ("hyb", 3, 1376, 256, 0),
+               ("hyb", 4, 256, 832, 0), ("3inst", 2, 128, 256, 0), ("1mad", 2, 128, 256, 0)]
+
+
+def t16(a):
+    return torch.from_numpy(a.view(np.int16)).to(DEV)
+
+
+@pytest.mark.parametrize("mode,K,m,n,rcp", LAYER_CASES)
+def test_bitshift_linear_forward_golden(golden, mode, K, m, n, rcp):
+    """Outputs of upstream BitshiftLinear.forward (CPU, plain layout) are the reference.  HYB layers run here
+    through the fused kernel on the same weights moved to the kernel layout (a pure byte shuffle plus the
+    fragment permutation of the tile elements, so the decoded matrix differs only by that permutation:
+    compare against the oracle on the kernel-layout matrix, and against upstream through the plain path)."""
+    g = golden("layer")
+    tag = f"{mode}_K{K}_{m}x{n}_rcp{rcp}"
+    codes, SU, SV, x, want = (g[f"{k}_{tag}"] for k in ("codes", "SU", "SV", "x", "y"))
+    tp = 8
+    hl, kl = ops.get_hadK(n // tp if rcp == 1 else n)
+    hr, kr = ops.get_hadK(m // tp if rcp == 2 else m)
+    hl, hr = (None if h is None else h.to(DEV) for h in (hl, hr))
+    tl = torch.from_numpy(g["tlut"]).to(DEV)
+    V = 2 if mode == "hyb" else 1
+    dm = "quantlut_sym" if mode == "hyb" else mode
+    # plain layout on the GPU == upstream's path
+    bl = BitshiftLinear(16, 16, 16, K, V, 9 if V == 2 else 0, dm, tlut=tl if V == 2 else None, has_kernel=False)
+    xs = torch.from_numpy(x).to(DEV)
+    if V == 1:
+        y = bl(xs, t16(codes), torch.from_numpy(SU).to(DEV), torch.from_numpy(SV).to(DEV), hl, hr, kl, kr, rcp, tp)
+        assert y.dtype == xs.dtype and y.shape == (x.shape[0], m)
+        assert rel_l2(y.float().cpu().numpy(), want.astype(np.float32)) < 1e-3
+        return
+    # HYB: decode of the plain layout is bit exact with upstream's matrix ...
+    Wp = bl.decode(t16(codes), m, n)
+    assert np.array_equal(Wp.cpu().numpy().view(np.uint16),
+                          O.decode_plain_layout(codes, m, n, K, 2, O.CODE_HYB, g["tlut"]).view(np.uint16))
+    # ... and the whole forward through the dense path matches upstream's output
+    bl.cb.K = K
+    xh = ops.rht(xs.reshape(-1, n // tp if rcp == 1 else n), sign_in=torch.from_numpy(SU).to(DEV),
+                 hadk_bits=ops.hadk_bits_for(hl, DEV), kfac=kl, transpose=True,
+                 scale=1 / (np.sqrt(n // tp if rcp == 1 else n) * 32), out_dtype=torch.float16).reshape(-1, n)
+    yy = (xh @ Wp.T).float()
+    out = ops.rht(yy.reshape(-1, m // tp if rcp == 2 else m), sign_out=torch.from_numpy(SV).to(DEV) * 32,
+                  hadk_bits=ops.hadk_bits_for(hr, DEV), kfac=kr, scale=1 / np.sqrt(m // tp if rcp == 2 else m))
+    assert rel_l2(out.reshape(-1, m).cpu().numpy(), want.astype(np.float32)) < 1e-3
+    # fused kernel on kernel-layout codes vs the oracle's forward on the same codes
+    if m % 32 == 0 and n % 32 == 0:
+        kc = O.plain_words_to_kernel_layout(codes, m, n, K)
+        blk = BitshiftLinear(16, 16, 16, K, 2, 9, "quantlut_sym", tlut=tl, has_kernel=True)
+        y = blk(xs, t16(kc), torch.from_numpy(SU).to(DEV), torch.from_numpy(SV).to(DEV), hl, hr, kl, kr, rcp, tp)
+        want_k = C.layer_forward(x.astype(np.float32), kc, m, n, K, g["tlut"], SU.astype(np.float32), SV,
+                                 None if hl is None else hl.cpu().numpy(), None if hr is None else hr.cpu().numpy(), rcp, tp)
+        assert y.dtype == torch.float16
+        assert rel_l2(y.float().cpu().numpy(), want_k) < 1e-3
+
+
+def test_layer4096_vs_upstream_output(golden):
+    """BASELINE configuration 1: 4096x4096, 2 bit, HYB, batch 1 - upstream's CPU forward output is the fixture."""
+    g = golden("layer4096")
+    lay = synth.make_layer(4096, 4096, 2, seed=1000)
+    q = QuantizedLinear(4096, 4096, 16, 16, 16, 2, 2, 9, "quantlut_sym").to(DEV)
+    q.trellis.copy_(t16(lay["codes"]))
+    q.tlut.copy_(torch.from_numpy(lay["tlut"]))
+    q.SU.copy_(torch.from_numpy(lay["SU"]))
+    q.SV.copy_(torch.from_numpy(lay["SV"]))
+    y = q(torch.from_numpy(lay["x"]).to(DEV))
+    assert y.shape == (1, 4096) and y.dtype == torch.float16
+    assert rel_l2(y.float().cpu().numpy(), g["y"]) < 1e-3
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("m,n", [(4096, 11008), (11008, 4096)])
+def test_quantized_linear_llama_shapes(K, m, n):
+    lay = synth.make_layer(m, n, K, seed=4000 + K)
+    q = QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, "quantlut_sym").to(DEV)
+    q.trellis.copy_(t16(lay["codes"]))
+    q.tlut.copy_(torch.from_numpy(lay["tlut"]))
+    q.SU.copy_(torch.from_numpy(lay["SU"]))
+    q.SV.copy_(torch.from_numpy(lay["SV"]))
+    y = q(torch.from_numpy(lay["x"]).to(DEV))
+    hl = None if q.had_left is None else q.had_left.cpu().numpy()
+    hr = None if q.had_right is None else q.had_right.cpu().numpy()
+    want = C.layer_forward(lay["x"].astype(np.float32), lay["codes"], m, n, K, lay["tlut"],
+                           lay["SU"].astype(np.float32), lay["SV"], hl, hr)
+    assert rel_l2(y.float().cpu().numpy(), want) < 1e-3
+
+
+def test_batched_forward_uses_dense_path():
+    m, n, K, bs = 512, 1024, 2, 16
+    lay = synth.make_layer(m, n, K, seed=77, bs=bs)
+    q = QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, "quantlut_sym").to(DEV)
+    q.trellis.copy_(t16(lay["codes"]))
+    q.tlut.copy_(torch.from_numpy(lay["tlut"]))
+    q.SU.copy_(torch.from_numpy(lay["SU"]))
+    q.SV.copy_(torch.from_numpy(lay["SV"]))
+    y = q(torch.from_numpy(lay["x"]).to(DEV))
+    want = C.layer_forward(lay["x"].astype(np.float32), lay["codes"], m, n, K, lay["tlut"],
+                           lay["SU"].astype(np.float32), lay["SV"])
+    assert rel_l2(y.float().cpu().numpy(), want) < 1e-3
+
+
+def test_legacy_entry_point_and_graph_capture():
+    """The upstream call sequence of lib/codebook/__init__.py:85-92, replayed from a CUDA graph."""
+    m, n, K = 4096, 4096, 2
+    lay = synth.make_layer(m, n, K, seed=9)
+    fn = getattr(qtip_kernels, f"decompress_matvec_16_9_{K}_1_{m}_1_{n}")
+    compressed = t16(lay["codes"]).reshape(-1).view(torch.int32)
+    x = torch.from_numpy(lay["x"]).to(DEV).T.contiguous()        # (n, 1) fp16
+    codebook = torch.from_numpy(lay["tlut"]).to(DEV).reshape(-1)
+    out = torch.zeros((m, 1), dtype=torch.float32, device=DEV)
+    fn(out, compressed, x, codebook)
+    want = C.matvec_kernel(lay["codes"], m, n, K, lay["tlut"], lay["x"])
+    assert rel_l2(out.T.cpu().numpy(), want) < 2e-6
+    first = out.clone()
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    ws = torch.zeros(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1), dtype=torch.uint8, device=DEV)
+    gph = torch.cuda.CUDAGraph()
+    out2 = torch.zeros((1, m), dtype=torch.float32, device=DEV)
+    with torch.cuda.stream(s):
+        ops.decompress_matvec(compressed, x.view(1, n), codebook, K, m, n, out=out2, workspace=ws)  # warm-up
+        torch.cuda.current_stream().synchronize()
+        with torch.cuda.graph(gph, stream=s):
+            ops.decompress_matvec(compressed, x.view(1, n), codebook, K, m, n, out=out2, workspace=ws)
+    out2.zero_()
+    gph.replay()
+    gph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out2.view(-1), first.view(-1))
+    with pytest.raises(RuntimeError):
+        fn(out, compressed, x.float(), codebook)

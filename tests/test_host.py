@@ -1,0 +1,59 @@
+"""CPU: host-side logic of the python mirrors (no kernels run)."""
+import numpy as np
+import pytest
+import torch
+
+from qtip_b200 import kernel_check, ops, qtip_kernels
+from qtip_b200.quantized_linear import QuantizedLinear
+
+
+def test_pack_hadk_round_trip():
+    for k in (12, 28, 52, 172):
+        h = ops.get_hadK(k * 4)[0]
+        bits = ops.pack_hadk(h).numpy().view(np.uint32)
+        assert bits.shape == (k, (k + 31) // 32)
+        un = ((bits[:, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(k, -1)[:, :k]
+        assert np.array_equal(un.astype(np.float32) * 2 - 1, h.numpy())
+
+
+def test_get_hadk_contract():
+    assert ops.get_hadK(4096) == (None, 1)
+    h, k = ops.get_hadK(11008)
+    assert k == 172 and h.shape == (172, 172) and h.dtype == torch.float32
+    ht, _ = ops.get_hadK(11008, transpose=True)
+    assert torch.equal(ht, h.T)
+    with pytest.raises(ValueError):
+        ops.get_hadK(172 * 3)
+
+
+def test_has_kernel_predicate():
+    assert kernel_check.has_kernel('quantlut_sym', 16, 2, 2, 9, 16, 16)
+    assert not kernel_check.has_kernel('3inst', 16, 2, 1, 0, 16, 16)
+    assert not kernel_check.has_kernel('quantlut_sym', 16, 5, 2, 9, 16, 16)
+    assert not kernel_check.has_kernel('quantlut_sym', 16, 2, 2, 8, 16, 16)
+
+
+def test_legacy_kernel_names_resolve():
+    f = qtip_kernels.decompress_matvec_16_9_2_1_4096_1_11008
+    assert callable(f) and f is qtip_kernels.decompress_matvec_16_9_2_1_4096_1_11008
+    with pytest.raises(AttributeError):
+        qtip_kernels.decompress_matvec_16_9_5_1_4096_1_4096
+    with pytest.raises(AttributeError):
+        qtip_kernels.decompress_matvec_16_8_2_1_4096_1_4096
+    with pytest.raises(AttributeError):
+        qtip_kernels.something_else
+    with pytest.raises(RuntimeError, match="CUDA"):
+        f(torch.zeros(4096, 1), torch.zeros(8, dtype=torch.int32), torch.zeros(11008, 1, dtype=torch.float16),
+          torch.zeros(1024, dtype=torch.float16))
+
+
+def test_quantized_linear_state_dict_keys():
+    q = QuantizedLinear(11008, 4096, 16, 16, 16, 2, 2, 9, 'quantlut_sym')
+    sd = q.state_dict()
+    assert set(sd) == {"rcp", "tp_rank", "trellis", "tlut", "SU", "SV"}
+    assert sd["trellis"].shape == (4096 // 16 * 11008 // 16, 32) and sd["trellis"].dtype == torch.int16
+    assert sd["tlut"].shape == (512, 2) and sd["tlut"].dtype == torch.float16
+    assert sd["SU"].dtype == torch.float16 and sd["SV"].dtype == torch.float32
+    assert q.K_left == 172 and q.K_right == 1 and q.has_kernel
+    q3 = QuantizedLinear(256, 256, 16, 16, 16, 2, 1, 0, '3inst')
+    assert q3.tlut is None and not q3.has_kernel
