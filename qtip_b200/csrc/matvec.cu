@@ -1,18 +1,20 @@
 // Fused trellis-decode + matvec (batch 1..8) for B200.
 //
-// Partition ("stream-K").  The packed matrix is a sequence of B = (m/32)*(n/32) blocks (a block is
-// a 2x2 group of 16x16 tiles, 128*K contiguous bytes; blocks of one 32-row block are contiguous).
-// The grid has one CTA per SM and CTA c owns the contiguous block range [c*B/G, (c+1)*B/G), so
-// every SM streams the same number of bytes (+-1 block) from one contiguous address range.  A
-// range is cut into "segments" at 32-row-block boundaries.
+// Partition.  The packed matrix is a sequence of B = (m/32)*(n/32) blocks (a block is a 2x2 group of
+// 16x16 tiles, 128*K contiguous bytes; the blocks of one 32-row block are contiguous).  The grid
+// has at most one CTA per SM.  Two schedules exist and the host picks the cheaper one per shape:
+//   rows     CTA c owns whole 32-row blocks c, c+G, ...: no cross-CTA reduction at all;
+//   stream-K CTA c owns the contiguous block range [c*B/G, (c+1)*B/G), cut into segments at
+//            row-block boundaries: perfectly balanced bytes, but row blocks shared by several
+//            CTAs need the ticket reduction below.
 //
-// Data path.  A producer warp streams the CTA's byte range through a ring of shared-memory
-// stages with cp.async.bulk (TMA, completion on an mbarrier per stage), running ahead of the
-// consumers across segment boundaries.  Sixteen consumer warps take the blocks of a stage
-// round-robin: a lane reads its 4K contiguous bytes and those of lane+1 (wrap-around bits) from
-// the stage, decodes 16 trellis states into four mma.m16n8k16 A fragments in registers - HYB:
-// h = s*(s+1), entry (h>>6)&511 of a LUT kept as 32 lane-private copies in shared memory, sign
-// flip from bit 15 - and multiplies them with x held in the B fragment (column j of B = batch row
+// Data path.  A producer warp streams the CTA's segments through a ring of shared-memory stages
+// with cp.async.bulk (TMA, completion on an mbarrier per stage), running ahead of the consumers
+// across segment boundaries.  31 consumer warps take the blocks of a stage two at a time: a lane
+// reads its 4K contiguous bytes and those of lane+1 (wrap-around bits) from the stage, decodes 16
+// trellis states into four mma.m16n8k16 A fragments in registers - HYB: h = s*(s+1), entry
+// (h>>6)&1023 of a 1024-entry table (the 512-entry LUT and its sign-flipped twin) kept as 32
+// lane-private copies in shared memory, so gathers never conflict - and multiplies them with x held in the B fragment (column j of B = batch row
 // j, so up to 8 batch rows ride along for free).  fp32 accumulation in the MMA.
 //
 // Reduction.  Warps of a CTA are summed through shared memory at the end of a segment.  When a
@@ -20,22 +22,33 @@
 // ticket; the CTA that draws the last ticket adds the partials in CTA order and writes the result,
 // so the output is deterministic and is overwritten, never accumulated into.
 //
+// Launch overlap.  The kernel is launched with programmatic stream serialization: everything that
+// touches only weights (barrier setup, LUT replication, the first ring fills) runs before
+// griddepcontrol.wait, i.e. while the previous kernel of the stream drains; x, out and the
+// workspace are touched only after it.
+//
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records an error code in
 // the workspace status word, raises a CTA-wide abort flag that makes all later waits fall through,
 // and the kernel runs to its end (with meaningless results) instead of hanging.
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace qtip {
 namespace {
 
-constexpr int kConsumerWarps = 16;
+constexpr int kConsumerWarps = 31;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
-constexpr int kStageBlocks = 32;                 // blocks per ring stage (two per consumer warp)
-constexpr int kLutBytes = 512 * 32 * 4;          // 512 entries x 32 lane-private copies x half2 = 64 KiB
-constexpr int kRedBytes = kConsumerWarps * 256 * 4;
+constexpr int kThreads = 1024;                   // 31 consumer warps + 1 producer warp
+constexpr int kStageBlocks = 2 * kConsumerWarps; // blocks per ring stage: two per consumer warp
+// Gather table: 1024 entries (sign bit of the hash folded in as the top index bit, so no separate
+// sign flip is needed) x 32 lane-private copies x half2 = 128 KiB.  Entry e, copy l at byte e*128 + l*4:
+// every lane reads its own bank, so a warp's 32 random lookups never conflict.
+constexpr int kLutBytes = 1024 * 32 * 4;
+constexpr int kCtrlBytes = 256;
+constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxStages = 8;
 constexpr int kMaxBatch = 8;
 constexpr unsigned kSpinLimit = 1u << 22;        // polls of ~20-40 ns each: gives up after ~0.1 s
@@ -47,7 +60,7 @@ constexpr unsigned kSpinLimit = 1u << 22;        // polls of ~20-40 ns each: giv
 constexpr size_t kCounterBytes = 64 * 1024;
 constexpr size_t kStatusOffset = kCounterBytes;
 constexpr size_t kPartialOffset = kCounterBytes + 256;
-constexpr int kMaxGrid = 256;  // sizing bound for the number of CTAs
+constexpr int kMaxGrid = 1024;  // sizing bound for the number of CTAs
 
 // A row block (nb consecutive blocks) meets at most floor(nb / minlen) CTAs that lie entirely inside
 // it plus two partial ones, where minlen = floor(B / G) is the shortest CTA range.
@@ -56,18 +69,29 @@ inline int max_contributors(long nb, long B, long G) {
     return (int)(nb / minlen) + 2;
 }
 
+enum { kModeStreamK = 1, kModeRows = 2 };
+
 struct Partition {
     int grid;       // CTAs
     int kmax;       // contributor slots per row block
-    long blocks;    // B
+    int mode;
 };
 
-Partition make_partition(int m, int n) {
+// Cost model in bytes streamed by the busiest SM; the ticket reduction of a shared row block costs
+// about as much time as streaming kTailBytes.
+constexpr long kTailBytes = 40 * 1024;
+
+Partition make_partition(int m, int n, int K) {
+    static const int forced = [] { const char *e = getenv("QTIP_MATVEC_MODE"); return e ? atoi(e) : 0; }();
     Partition p;
-    p.blocks = (long)(m >> 5) * (n >> 5);
-    const long sms = sm_count();
-    p.grid = (int)(p.blocks < sms ? p.blocks : sms);
-    p.kmax = max_contributors(n >> 5, p.blocks, p.grid);
+    const long mb = m >> 5, nb = n >> 5, B = mb * nb, sms = sm_count(), bb = 128 * K;
+    const long g_stream = B < sms ? B : sms, g_rows = mb < sms ? mb : sms;
+    const long cost_rows = ((mb + g_rows - 1) / g_rows) * nb * bb;
+    const bool shared_rows = (B % g_stream) != 0 || ((B / g_stream) % nb) != 0;
+    const long cost_stream = ((B + g_stream - 1) / g_stream) * bb + (shared_rows ? kTailBytes : 0);
+    p.mode = forced ? forced : (cost_rows <= cost_stream ? kModeRows : kModeStreamK);
+    p.grid = (int)(p.mode == kModeRows ? g_rows : g_stream);
+    p.kmax = max_contributors(nb, B, g_stream);
     return p;
 }
 
@@ -111,209 +135,296 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+// A lane's 4K bytes of a block staged in shared memory.
+template <int K>
+__device__ __forceinline__ LaneCodes<K> lds_lane_codes(uint32_t addr) {
+    LaneCodes<K> c;
+    if constexpr (K == 2) {
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(c.w[0]), "=r"(c.w[1]) : "r"(addr) : "memory");
+    } else if constexpr (K == 3) {
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(c.w[0]) : "r"(addr) : "memory");
+        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(c.w[1]) : "r"(addr) : "memory");
+        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(c.w[2]) : "r"(addr) : "memory");
+    } else {
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(c.w[0]), "=r"(c.w[1]), "=r"(c.w[2]), "=r"(c.w[3])
+                     : "r"(addr)
+                     : "memory");
+    }
+    return c;
 }
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// ---- partition arithmetic (identical on host and device) ------------------------------------------------
+// ---- partition arithmetic -------------------------------------------------------------------------------
 __host__ __device__ __forceinline__ long range_start(long c, long B, long G) { return c * B / G; }
 __host__ __device__ __forceinline__ long cta_of_block(long b, long B, long G) { return ((b + 1) * G - 1) / B; }
 
-struct Shared {            // small control block at the start of dynamic shared memory
+// The segments (row block M, blocks [s0, s1) in the global block numbering) of one CTA, in order.
+struct SegmentIter {
+    long nb, end, pos, step;  // rows mode: pos = M*nb, step = G*nb;  stream-K: pos walks [r0, r1)
+    int mode;
+    __device__ __forceinline__ SegmentIter(int mode_, long mb, long nb_, long G, long c) : nb(nb_), mode(mode_) {
+        if (mode == kModeRows) { pos = c * nb; end = mb * nb; step = G * nb; }
+        else { const long B = mb * nb; pos = range_start(c, B, G); end = range_start(c + 1, B, G); step = 0; }
+    }
+    __device__ __forceinline__ bool next(long &s0, long &s1) {
+        if (pos >= end) return false;
+        s0 = pos;
+        if (mode == kModeRows) { s1 = pos + nb; pos += step; }
+        else { s1 = min(end, (pos / nb + 1) * nb); pos = s1; }
+        return true;
+    }
+};
+
+struct Shared {            // control block at the start of dynamic shared memory
     unsigned long long full[kMaxStages];
     unsigned long long empty[kMaxStages];
-    uint32_t stage_addr[kMaxStages];
     int abort_flag;
     int is_last;
 };
+static_assert(sizeof(Shared) <= kCtrlBytes, "control block too large");
 
-// Cross-warp sum of the per-warp 32x8 accumulators of one segment, then the final store or the
-// partial-sum / ticket protocol.  Consumer threads only.
+// Cross-warp sum of the per-warp 32 x 8 accumulators of one segment, then the final store or the
+// partial-sum / ticket protocol.  Consumer threads only (NW warps).  Only the first `bs` batch
+// columns are kept: red holds [NW][bs][32] floats.
+template <int NW>
 __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, Shared *sh, float *__restrict__ out,
                                                float *__restrict__ partial, unsigned *__restrict__ counters, long M,
-                                               long nb, long B, long G, int kmax, int m, int bs) {
+                                               long nb, long B, long G, int kmax, int m, int bs, bool whole_row) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int stride = 32 * bs;
     // accumulator (ms, i): row = 16*ms + g + 8*(i>>1), batch = 2*t + (i&1); slot = batch*32 + row
 #pragma unroll
     for (int ms = 0; ms < 2; ms++)
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            red[warp * 256 + (2 * t + (i & 1)) * 32 + 16 * ms + g + 8 * (i >> 1)] = acc[ms][i];
-    consumer_sync();
+        for (int i = 0; i < 4; i++) {
+            const int batch = 2 * t + (i & 1);
+            if (batch < bs) red[warp * stride + batch * 32 + 16 * ms + g + 8 * (i >> 1)] = acc[ms][i];
+        }
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
     float v = 0.f;
-    if (tid < 256) {
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; w++) v += red[w * 256 + tid];
+    if (tid < stride) {
+#pragma unroll 4
+        for (int w = 0; w < NW; w++) v += red[w * stride + tid];
     }
     const int b = tid >> 5, r = tid & 31;
-    const long c_first = cta_of_block(M * nb, B, G), c_last = cta_of_block((M + 1) * nb - 1, B, G);
-    const int contributors = (int)(c_last - c_first) + 1;
+    int contributors = 1;
+    long c_first = 0;
+    if (!whole_row) {
+        c_first = cta_of_block(M * nb, B, G);
+        contributors = (int)(cta_of_block((M + 1) * nb - 1, B, G) - c_first) + 1;
+    }
     if (contributors == 1) {
-        if (tid < 256 && b < bs) out[(size_t)b * m + 32 * M + r] = v;
-        consumer_sync();
+        if (tid < stride) out[(size_t)b * m + 32 * M + r] = v;
+        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
         return;
     }
     const int k = (int)(blockIdx.x - c_first);
     float *slot = partial + ((size_t)M * kmax) * 256;
-    if (tid < 256) __stcg(slot + (size_t)k * 256 + tid, v);
+    if (tid < stride) __stcg(slot + (size_t)k * 256 + tid, v);
     __threadfence();
-    consumer_sync();
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
     if (tid == 0) {
         unsigned prev = atomicAdd(&counters[M], 1u);
         sh->is_last = (prev == (unsigned)(contributors - 1));
     }
-    consumer_sync();
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
     if (sh->is_last) {
         __threadfence();
-        if (tid < 256 && b < bs) {
+        if (tid < stride) {
             float s = 0.f;
             for (int c = 0; c < contributors; c++) s += __ldcg(slot + (size_t)c * 256 + tid);
             out[(size_t)b * m + 32 * M + r] = s;
         }
         if (tid == 0) counters[M] = 0;  // leave the workspace ready for the next call
     }
-    consumer_sync();
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+}
+
+// The four states of tile tt (= ks*2 + ms) of a lane, from the lane's own words and those of lane+1.
+// Only the low 16 bits of each st[q] are meaningful (the hash ignores the rest), which saves the
+// masks and, for the state that already sits in the low half of a word, the shift.  Shifts are
+// funnel shifts of (own : next) so no 64-bit value is ever formed.
+template <int K>
+__device__ __forceinline__ void tile_states(const LaneCodes<K> &own, const LaneCodes<K> &nxt, int tt, uint32_t (&st)[4]) {
+    if constexpr (K == 2) {
+        // word ks holds slice(ms=1) << 16 | slice(ms=0); state q = low 16 bits of (own slice << 4q | next slice >> (16-4q))
+        const uint32_t w = own.w[tt >> 1], nw = nxt.w[tt >> 1];
+        if ((tt & 1) == 0) {
+            const uint32_t lo = nw << 16;  // next slice in the top half
+            st[0] = w; st[1] = __funnelshift_l(lo, w, 4); st[2] = __funnelshift_l(lo, w, 8); st[3] = __funnelshift_l(lo, w, 12);
+        } else {
+            const uint32_t hi = w >> 16;   // nw already has the next slice in its top half
+            st[0] = hi; st[1] = __funnelshift_l(nw, hi, 4); st[2] = __funnelshift_l(nw, hi, 8); st[3] = __funnelshift_l(nw, hi, 12);
+        }
+    } else if constexpr (K == 3) {
+        // 24-bit slices at byte offset 3*tt.  S: own slice in the low 24 bits (junk above is shifted
+        // out); N: next slice with its top 16 bits in the top half of the register.
+        uint32_t S, N;
+        if (tt == 0) { S = own.w[0]; N = nxt.w[0] << 8; }
+        else if (tt == 1) { S = __funnelshift_r(own.w[0], own.w[1], 24); N = __funnelshift_r(nxt.w[0], nxt.w[1], 16); }
+        else if (tt == 2) { S = __funnelshift_r(own.w[1], own.w[2], 16); N = __funnelshift_r(nxt.w[1], nxt.w[2], 8); }
+        else { S = own.w[2] >> 8; N = nxt.w[2]; }
+        // window bit 47 = first bit of S; state q = window bits [47-6q .. 32-6q]
+        st[0] = S >> 8; st[1] = S >> 2; st[2] = __funnelshift_l(N, S, 4); st[3] = __funnelshift_l(N, S, 10);
+    } else {
+        const uint32_t S = own.w[tt], N = nxt.w[tt];
+        st[0] = S >> 16; st[1] = S >> 8; st[2] = S; st[3] = __funnelshift_l(N, S, 8);
+    }
+}
+
+// One HYB lookup: h = t*t + t; entry = h bits 15..6 (bit 15 = sign flip of the first weight, folded
+// into the table); 128 bytes per entry, the lane's copy selected by lut_lane.  Two of the four
+// instructions are integer multiply-adds, which issue at full rate; logic ops are half rate.
+__device__ __forceinline__ uint32_t hyb_lookup(uint32_t t, uint32_t lut_lane) {
+    uint32_t w;
+    asm("{\n\t.reg .b32 h, a;\n\t"
+        "mad.lo.u32 h, %1, %1, %1;\n\t"
+        "and.b32 h, h, 0xFFC0;\n\t"
+        "mad.lo.u32 a, h, 2, %2;\n\t"
+        "ld.shared.u32 %0, [a];\n\t}"
+        : "=r"(w)
+        : "r"(t), "r"(lut_lane));
+    return w;
+}
+
+// 16 states of one lane -> four A fragments -> four MMAs (2 k-subtiles x 2 m-subtiles).
+template <int K>
+__device__ __forceinline__ void decode_block(const LaneCodes<K> &own, const LaneCodes<K> &nxt, const uint32_t (&xb)[4],
+                                             float (&acc)[2][4], uint32_t lut_lane) {
+#pragma unroll
+    for (int tt = 0; tt < 4; tt++) {
+        const int ks = tt >> 1, ms = tt & 1;
+        uint32_t st[4], a[4];
+        tile_states<K>(own, nxt, tt, st);
+#pragma unroll
+        for (int q = 0; q < 4; q++) a[q] = hyb_lookup(st[q], lut_lane);
+        mma_16816(acc[ms], a, xb[2 * ks], xb[2 * ks + 1]);
+    }
 }
 
 template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
     matvec_hyb_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
-                      const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int nstages,
-                      uint8_t *__restrict__ workspace, uint32_t smem_total) {
+                      const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int mode, int nstages,
+                      uint8_t *__restrict__ workspace) {
     constexpr int kBlockBytes = 128 * K;
     constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     extern __shared__ __align__(128) uint8_t smem[];
+    // layout: control block | LUT | ring stages | cross-warp reduction buffer [31][bs][32] fp32
+    Shared *sh = reinterpret_cast<Shared *>(smem);
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kCtrlBytes);
+    const uint32_t ring = smem_u32(smem + kCtrlBytes + kLutBytes);
+    float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes + nstages * kStageBytes);
 
     unsigned *counters = reinterpret_cast<unsigned *>(workspace);
     unsigned *status = reinterpret_cast<unsigned *>(workspace + kStatusOffset);
     float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
 
-    // ---- carve shared memory.  The LUT must sit on a 64 KiB boundary of the shared window so that a
-    // gather address is (hash bits) | (lane*4): one logic op, no add.  Whatever lies below and above
-    // it holds the control block, the cross-warp reduction buffer and the ring stages.
-    const uint32_t base = smem_u32(smem);
-    const uint32_t lut_addr = (base + 0xFFFFu) & ~0xFFFFu;
-    Shared *sh = reinterpret_cast<Shared *>(smem);  // control block first if it fits below the LUT, else above
-    uint32_t lo = base, lo_end = lut_addr, hi = lut_addr + kLutBytes, hi_end = base + smem_total;
-    auto carve = [&](uint32_t bytes) -> uint32_t {
-        bytes = (bytes + 127u) & ~127u;
-        if (lo + bytes <= lo_end) { uint32_t a = lo; lo += bytes; return a; }
-        uint32_t a = hi; hi += bytes; return a;  // host sized smem_total so that this fits
-    };
-    const uint32_t sh_addr = carve(sizeof(Shared));
-    const uint32_t red_addr = carve(kRedBytes);
-    sh = reinterpret_cast<Shared *>(smem + (sh_addr - base));
-    float *red = reinterpret_cast<float *>(smem + (red_addr - base));
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; s++) {
-            sh->stage_addr[s] = carve(kStageBytes);
             mbar_init(smem_u32(&sh->full[s]), 1);
             mbar_init(smem_u32(&sh->empty[s]), kConsumerWarps);
         }
         sh->abort_flag = 0;
         sh->is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (hi > hi_end) atomicCAS(status, 0u, 3u);  // cannot happen when the host sizes smem_total
     }
     __syncthreads();
+    grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
 
-    const long nb = n >> 5;
-    const long B = (long)(m >> 5) * nb, G = gridDim.x;
-    const long r0 = range_start(blockIdx.x, B, G), r1 = range_start(blockIdx.x + 1, B, G);
+    const int nb = n >> 5, mb = m >> 5;
+    const int G = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &sh->abort_flag;
 
     if (warp == kConsumerWarps) {
         // ------------------------------- producer warp ---------------------------------------------
+        // reads only the packed codes (weights), so it does not wait for the previous kernel
         if (lane == 0) {
-            uint32_t it = 0;
-            for (long seg0 = r0; seg0 < r1;) {
-                const long seg1 = min(r1, (seg0 / nb + 1) * nb);
-                for (long b = seg0; b < seg1 && !*abort_flag; b += kStageBlocks, it++) {
-                    const uint32_t cnt = (uint32_t)min((long)kStageBlocks, seg1 - b);
-                    const uint32_t s = it % nstages, round = it / nstages;
+            uint32_t s = 0, round = 0;  // ring slot, number of times the ring wrapped
+            SegmentIter segs(mode, mb, nb, G, blockIdx.x);
+            long seg0, seg1;
+            while (segs.next(seg0, seg1)) {
+                const uint8_t *src = codes + (size_t)seg0 * kBlockBytes;
+                for (int left = (int)(seg1 - seg0); left > 0 && !*abort_flag; left -= kStageBlocks) {
+                    const uint32_t bytes = (uint32_t)min(kStageBlocks, left) * kBlockBytes;
                     if (round > 0) mbar_wait(smem_u32(&sh->empty[s]), (round - 1) & 1, abort_flag, status, 1);
                     const uint32_t bar = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(bar, cnt * kBlockBytes);
-                    bulk_g2s(sh->stage_addr[s], codes + (size_t)b * kBlockBytes, cnt * kBlockBytes, bar);
+                    mbar_expect_tx(bar, bytes);
+                    bulk_g2s(ring + s * kStageBytes, src, bytes, bar);
+                    src += kStageBytes;
+                    if (++s == (uint32_t)nstages) { s = 0; round++; }
                 }
-                seg0 = seg1;
             }
         }
-        return;  // every copy issued above is consumed (waited for) by the consumer warps below
+        return;  // every copy issued above is waited for by the consumer warps below
     }
 
     // ------------------------------------ consumer warps ------------------------------------------------
-    // lane-private LUT copies: entry e, copy l at byte e*128 + l*4 -> conflict-free gathers
-    {
-        uint32_t *lut = reinterpret_cast<uint32_t *>(smem + (lut_addr - base));
-        for (int i = threadIdx.x; i < 512 * 8; i += kConsumerThreads) {
-            const uint32_t e = tlut[i >> 3];
-            reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
-        }
+    // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
+    // flips the sign of the first (low) half of the pair
+    for (int i = threadIdx.x; i < 1024 * 8; i += kConsumerThreads) {
+        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
+        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
     }
     consumer_sync();
+    grid_dependency_wait();  // x, out and the workspace belong to the stream's data flow
 
     const int g = lane >> 2, t = lane & 3;
     const bool xvalid = g < bs;
-    const __half *xrow = x + (size_t)(xvalid ? g : 0) * n + 2 * t;
-    const uint32_t lut_lane = lut_addr + lane * 4;
+    const uint32_t *xrow = reinterpret_cast<const uint32_t *>(x + (size_t)(xvalid ? g : 0) * n + 2 * t);
+    const uint32_t lut_lane = smem_u32(lut) + lane * 4;
     const uint32_t own_off = lane * (4 * K), nxt_off = ((lane + 1) & 31) * (4 * K);
+    const uint32_t off0 = warp * kBlockBytes, off1 = (warp + kConsumerWarps) * kBlockBytes;
 
-    uint32_t it = 0;
-    for (long seg0 = r0; seg0 < r1;) {
-        const long M = seg0 / nb;
-        const long seg1 = min(r1, (M + 1) * nb);
+    uint32_t s = 0, phase = 0;  // ring slot and the parity its "full" barrier completes next
+    SegmentIter segs(mode, mb, nb, G, blockIdx.x);
+    long seg0, seg1;
+    while (segs.next(seg0, seg1)) {
+        const int M = (int)(seg0 / nb);
         float acc[2][4] = {};
-        for (long b = seg0; b < seg1; b += kStageBlocks, it++) {
-            const int cnt = (int)min((long)kStageBlocks, seg1 - b);
-            const uint32_t s = it % nstages, round = it / nstages;
-            mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, status, 2);
-            const uint32_t stage = sh->stage_addr[s];
-#pragma unroll 2
-            for (int j = warp; j < cnt; j += kConsumerWarps) {
-                const int N = (int)(b + j - M * nb);
-                uint32_t xb[4] = {0u, 0u, 0u, 0u};  // [ks][cols 2t,2t+1 | cols 2t+8,2t+9]
-                if (xvalid) {
-                    const uint32_t *xp = reinterpret_cast<const uint32_t *>(xrow + 32 * N);
-                    xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12);
-                }
-                LaneCodes<K> own, nxt;
-                const uint32_t blk = stage + j * kBlockBytes;
-#pragma unroll
-                for (int i = 0; i < K; i++) {
-                    own.w[i] = lds_u32(blk + own_off + 4 * i);
-                    nxt.w[i] = lds_u32(blk + nxt_off + 4 * i);
-                }
-#pragma unroll
-                for (int tt = 0; tt < 4; tt++) {
-                    const int ks = tt >> 1, ms = tt & 1;
-                    uint32_t st[4], a[4];
-                    lane_states<K>(lane_slice<K>(own, tt), lane_slice<K>(nxt, tt), st);
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const uint32_t h = hyb_hash(st[q]);
-                        a[q] = lds_u32(((h << 1) & 0xFF80u) | lut_lane) ^ (h & 0x8000u);
-                    }
-                    mma_16816(acc[ms], a, xb[2 * ks], xb[2 * ks + 1]);
-                }
+        // this warp's first block of the stage, as 32-column index inside the row block
+        const uint32_t *xp = xrow + 16 * ((int)(seg0 - (long)M * nb) + warp);
+        for (int left = (int)(seg1 - seg0); left > 0; left -= kStageBlocks) {
+            const bool v0 = warp < left, v1 = warp + kConsumerWarps < left;
+            // x fragments do not depend on the stage: issue them before waiting
+            uint32_t xb0[4] = {0u, 0u, 0u, 0u}, xb1[4] = {0u, 0u, 0u, 0u};  // [ks][cols 2t,2t+1 | cols 2t+8,2t+9]
+            if (xvalid) {
+                if (v0) { xb0[0] = __ldg(xp); xb0[1] = __ldg(xp + 4); xb0[2] = __ldg(xp + 8); xb0[3] = __ldg(xp + 12); }
+                const uint32_t *xq = xp + 16 * kConsumerWarps;
+                if (v1) { xb1[0] = __ldg(xq); xb1[1] = __ldg(xq + 4); xb1[2] = __ldg(xq + 8); xb1[3] = __ldg(xq + 12); }
             }
+            xp += 16 * kStageBlocks;
+            mbar_wait(smem_u32(&sh->full[s]), phase, abort_flag, status, 2);
+            const uint32_t stage = ring + s * kStageBytes;
+            LaneCodes<K> own0 = {}, nxt0 = {}, own1 = {}, nxt1 = {};
+            if (v0) {
+                own0 = lds_lane_codes<K>(stage + off0 + own_off);
+                nxt0 = lds_lane_codes<K>(stage + off0 + nxt_off);
+            }
+            if (v1) {
+                own1 = lds_lane_codes<K>(stage + off1 + own_off);
+                nxt1 = lds_lane_codes<K>(stage + off1 + nxt_off);
+            }
+            // the stage's bytes are in registers: hand it back to the producer before decoding
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
+            if (++s == (uint32_t)nstages) { s = 0; phase ^= 1; }
+            if (v0) decode_block<K>(own0, nxt0, xb0, acc, lut_lane);
+            if (v1) decode_block<K>(own1, nxt1, xb1, acc, lut_lane);
         }
-        finish_segment(acc, red, sh, out, partial, counters, M, nb, B, G, kmax, m, bs);
-        seg0 = seg1;
+        finish_segment<kConsumerWarps>(acc, red, sh, out, partial, counters, M, nb, (long)mb * nb, G, kmax, m, bs,
+                                       mode == kModeRows);
     }
     if (*abort_flag) {
         // a wait gave up: give copies that may still be in flight time to land before the CTA retires
@@ -351,13 +462,15 @@ __device__ __forceinline__ uint64_t tile_bits48(const uint16_t *__restrict__ wor
     return (v << (pos & 15)) >> 16;
 }
 
+constexpr int kPlainWarps = 16;
+
 template <int CODE>
-__global__ void __launch_bounds__(kConsumerThreads, 1)
+__global__ void __launch_bounds__(kPlainWarps * 32, 2)
     matvec_plain_kernel(float *__restrict__ out, const uint16_t *__restrict__ codes, const __half *__restrict__ x, int K,
-                        int m, int n, int bs, int kmax, uint8_t *__restrict__ workspace) {
+                        int m, int n, int bs, int kmax, int mode, uint8_t *__restrict__ workspace) {
     extern __shared__ __align__(128) uint8_t smem[];
     Shared *sh = reinterpret_cast<Shared *>(smem);
-    float *red = reinterpret_cast<float *>(smem + 256);
+    float *red = reinterpret_cast<float *>(smem + kCtrlBytes);
     unsigned *counters = reinterpret_cast<unsigned *>(workspace);
     float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -365,16 +478,16 @@ __global__ void __launch_bounds__(kConsumerThreads, 1)
     const int g = lane >> 2, t = lane & 3;
     const bool xvalid = g < bs;
     const __half *xrow = x + (size_t)(xvalid ? g : 0) * n;
-    const long nb = n >> 5;
-    const long B = (long)(m >> 5) * nb, G = gridDim.x;
-    const long r0 = range_start(blockIdx.x, B, G), r1 = range_start(blockIdx.x + 1, B, G);
+    const long nb = n >> 5, mb = m >> 5;
+    const long B = mb * nb, G = gridDim.x;
 
-    for (long seg0 = r0; seg0 < r1;) {
+    SegmentIter segs(mode, mb, nb, G, blockIdx.x);
+    long seg0, seg1;
+    while (segs.next(seg0, seg1)) {
         const long M = seg0 / nb;
-        const long seg1 = min(r1, (M + 1) * nb);
         float acc[2][4] = {};
         const int kt0 = 2 * (int)(seg0 - M * nb), kt1 = 2 * (int)(seg1 - M * nb);
-        for (int kt = kt0 + warp; kt < kt1; kt += kConsumerWarps) {
+        for (int kt = kt0 + warp; kt < kt1; kt += kPlainWarps) {
             uint32_t b0 = 0u, b1 = 0u;
             if (xvalid) {
                 const uint32_t *xp = reinterpret_cast<const uint32_t *>(xrow + 16 * kt + 4 * t);
@@ -396,8 +509,7 @@ __global__ void __launch_bounds__(kConsumerThreads, 1)
                 mma_16816(acc[ms], a, b0, b1);
             }
         }
-        finish_segment(acc, red, sh, out, partial, counters, M, nb, B, G, kmax, m, bs);
-        seg0 = seg1;
+        finish_segment<kPlainWarps>(acc, red, sh, out, partial, counters, M, nb, B, G, kmax, m, bs, mode == kModeRows);
     }
 }
 
@@ -414,26 +526,32 @@ template <int K>
 int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
                uint8_t *workspace, cudaStream_t s) {
     constexpr int kStageBytes = kStageBlocks * 128 * K;
-    // ring depth: about 64 KiB in flight per SM
-    constexpr int nstages = (64 * 1024 / kStageBytes) < kMaxStages ? (64 * 1024 / kStageBytes) : kMaxStages;
-    // worst case the LUT alignment wastes just under 64 KiB below it only if nothing fits there; the
-    // carve order (control, reduction buffer, stages) fills the low part first, so size for: slack to
-    // the boundary + LUT + everything else
-    constexpr uint32_t payload = 256 + kRedBytes + nstages * kStageBytes;  // control block, reduction buffer, ring
-    constexpr uint32_t smem_total = 64 * 1024 + kLutBytes + payload > 227 * 1024 ? 227 * 1024
-                                                                                   : 64 * 1024 + kLutBytes + payload;
-    static_assert(kLutBytes + payload + 1024 + kStageBytes <= 227 * 1024, "ring does not fit");
+    // the ring gets whatever the table and the reduction buffer leave: 2 to 4 stages of 15.5 KiB * K/2
+    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
+    int nstages = (kSmemLimit - kCtrlBytes - kLutBytes - red_bytes) / kStageBytes;
+    if (nstages > kMaxStages) nstages = kMaxStages;
+    if (nstages < 2) return QTIP_ERR_BAD_ARG;
+    const int smem_total = kCtrlBytes + kLutBytes + nstages * kStageBytes + red_bytes;
     static bool attr_set[64] = {};
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)smem_total));
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
         attr_set[dev] = true;
     }
-    const Partition p = make_partition(m, n);
-    matvec_hyb_kernel<K><<<p.grid, kThreads, smem_total, s>>>(out, codes, x, tlut, m, n, bs, p.kmax, nstages, workspace,
-                                                             smem_total);
+    const Partition p = make_partition(m, n, K);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_total;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode, nstages,
+                                     workspace));
     return check_launch();
 }
 
@@ -471,15 +589,23 @@ extern "C" int qtip_decompress_matvec_plain(float *out, const void *codes, const
     if (code != QTIP_CODE_3INST && code != QTIP_CODE_1MAD) return QTIP_ERR_BAD_ARG;
     int st = check_common(out, codes, x, K, m, n, bs, workspace, workspace_bytes);
     if (st != QTIP_OK) return st;
-    const Partition p = make_partition(m, n);
+    Partition p = make_partition(m, n, K);
+    // two CTAs of 16 warps per SM
+    if (p.mode == kModeStreamK) {
+        const long B = (long)(m >> 5) * (n >> 5);
+        p.grid = (int)(B < 2L * p.grid ? B : 2L * p.grid);
+        p.kmax = max_contributors(n >> 5, B, p.grid);
+    }
     auto *c = static_cast<const uint16_t *>(codes);
     auto *xh = static_cast<const __half *>(x);
     auto *ws = static_cast<uint8_t *>(workspace);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    constexpr int smem = 256 + kRedBytes;
+    const int smem = kCtrlBytes + kPlainWarps * 32 * bs * 4;
     if (code == QTIP_CODE_3INST)
-        matvec_plain_kernel<QTIP_CODE_3INST><<<p.grid, kConsumerThreads, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax, ws);
+        matvec_plain_kernel<QTIP_CODE_3INST><<<p.grid, kPlainWarps * 32, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax,
+                                                                                  p.mode, ws);
     else
-        matvec_plain_kernel<QTIP_CODE_1MAD><<<p.grid, kConsumerThreads, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax, ws);
+        matvec_plain_kernel<QTIP_CODE_1MAD><<<p.grid, kPlainWarps * 32, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax,
+                                                                                 p.mode, ws);
     return check_launch();
 }
