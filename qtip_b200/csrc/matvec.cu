@@ -39,10 +39,10 @@
 namespace qtip {
 namespace {
 
-constexpr int kConsumerWarps = 31;
+constexpr int kConsumerWarps = 32;               // all 32 warps decode; lane 0 of warp 0 also feeds the ring
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = 1024;                   // 31 consumer warps + 1 producer warp
-constexpr int kStageBlocks = 2 * kConsumerWarps; // blocks per ring stage: two per consumer warp
+constexpr int kThreads = 1024;
+constexpr int kStageBlocks = 2 * kConsumerWarps; // blocks per ring stage: two per warp
 // Gather table: 1024 entries (sign bit of the hash folded in as the top index bit, so no separate
 // sign flip is needed) x 32 lane-private copies x half2 = 128 KiB.  Entry e, copy l at byte e*128 + l*4:
 // every lane reads its own bank, so a warp's 32 random lookups never conflict.
@@ -134,7 +134,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -189,16 +188,22 @@ struct Shared {            // control block at the start of dynamic shared memor
     unsigned long long empty[kMaxStages];
     int abort_flag;
     int is_last;
+    // cursor of the ring producer (touched by thread 0 only)
+    long p_pos, p_end, p_step, p_seg_end;   // next block to fetch; end of the CTA's work; rows-mode stride; end of the current segment
+    unsigned p_slot, p_round;
 };
 static_assert(sizeof(Shared) <= kCtrlBytes, "control block too large");
 
 // Cross-warp sum of the per-warp 32 x 8 accumulators of one segment, then the final store or the
 // partial-sum / ticket protocol.  Consumer threads only (NW warps).  Only the first `bs` batch
 // columns are kept: red holds [NW][bs][32] floats.
+// trailing_sync = false is allowed only when the caller alternates between two `red` buffers, so
+// that the next segment's stores cannot overtake this segment's readers.
 template <int NW>
 __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, Shared *sh, float *__restrict__ out,
                                                float *__restrict__ partial, unsigned *__restrict__ counters, long M,
-                                               long nb, long B, long G, int kmax, int m, int bs, bool whole_row) {
+                                               long nb, long B, long G, int kmax, int m, int bs, bool whole_row,
+                                               bool trailing_sync = true) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int stride = 32 * bs;
@@ -225,7 +230,7 @@ __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, S
     }
     if (contributors == 1) {
         if (tid < stride) out[(size_t)b * m + 32 * M + r] = v;
-        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+        if (trailing_sync) asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
         return;
     }
     const int k = (int)(blockIdx.x - c_first);
@@ -312,7 +317,38 @@ __device__ __forceinline__ void decode_block(const LaneCodes<K> &own, const Lane
     }
 }
 
+// Ring producer step (thread 0 only): fetch the next stage of this CTA's work, if any, into ring slot
+// p_slot.  A slot may be refilled once all 32 warps have pulled their bytes of its previous use.
 template <int K>
+__device__ __forceinline__ void produce_stage(Shared *sh, const uint8_t *__restrict__ codes, uint32_t ring, int nstages,
+                                              int mode, long nb, unsigned *status) {
+    constexpr int kBlockBytes = 128 * K;
+    constexpr int kStageBytes = kStageBlocks * kBlockBytes;
+    long pos = sh->p_pos;
+    if (pos >= sh->p_end) return;
+    volatile int *abort_flag = &sh->abort_flag;
+    if (*abort_flag) return;
+    long seg_end = sh->p_seg_end;
+    if (pos >= seg_end) {  // open the next segment
+        if (mode == kModeRows) { pos += sh->p_step - nb; seg_end = pos + nb; if (pos >= sh->p_end) { sh->p_pos = pos; return; } }
+        else seg_end = min(sh->p_end, (pos / nb + 1) * nb);
+        sh->p_seg_end = seg_end;
+    }
+    const unsigned slot = sh->p_slot, round = sh->p_round;
+    if (round > 0) mbar_wait(smem_u32(&sh->empty[slot]), (round - 1) & 1, abort_flag, status, 1);
+    const uint32_t bytes = (uint32_t)min((long)kStageBlocks, seg_end - pos) * kBlockBytes;
+    const uint32_t bar = smem_u32(&sh->full[slot]);
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(ring + slot * kStageBytes, codes + (size_t)pos * kBlockBytes, bytes, bar);
+    sh->p_pos = pos + min((long)kStageBlocks, seg_end - pos);
+    if (slot + 1 == (unsigned)nstages) { sh->p_slot = 0; sh->p_round = round + 1; }
+    else sh->p_slot = slot + 1;
+}
+
+// XS: x is staged once per CTA in shared memory, permuted so that a lane's four B-fragment words of
+// a block are one 16-byte load; otherwise they are read from global memory (L1-resident) per block.
+// DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
+template <int K, bool XS, bool DB>
 __global__ void __launch_bounds__(kThreads, 1)
     matvec_hyb_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
                       const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int mode, int nstages,
@@ -320,15 +356,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int kBlockBytes = 128 * K;
     constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: control block | LUT | ring stages | cross-warp reduction buffer [31][bs][32] fp32
+    // layout: control block | LUT | ring stages | reduction buffer(s) [32][bs][32] fp32 | x (bs, n) fp16 permuted
     Shared *sh = reinterpret_cast<Shared *>(smem);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kCtrlBytes);
     const uint32_t ring = smem_u32(smem + kCtrlBytes + kLutBytes);
+    const int red_floats = kConsumerWarps * 32 * bs;
     float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes + nstages * kStageBytes);
+    uint4 *xs = reinterpret_cast<uint4 *>(red + (DB ? 2 : 1) * red_floats);
 
     unsigned *counters = reinterpret_cast<unsigned *>(workspace);
     unsigned *status = reinterpret_cast<unsigned *>(workspace + kStatusOffset);
     float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
+
+    const int nb = n >> 5, mb = m >> 5;
+    const int G = gridDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; s++) {
@@ -337,94 +379,88 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         sh->abort_flag = 0;
         sh->is_last = 0;
+        SegmentIter it(mode, mb, nb, G, blockIdx.x);
+        sh->p_pos = it.pos; sh->p_end = it.end; sh->p_step = it.step;
+        sh->p_seg_end = mode == kModeRows ? it.pos + nb : min(it.end, (it.pos / nb + 1) * nb);
+        sh->p_slot = 0; sh->p_round = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // fill the ring: packed codes are weights, no need to wait for the previous kernel
+        for (int s = 0; s < nstages; s++) produce_stage<K>(sh, codes, ring, nstages, mode, nb, status);
     }
-    __syncthreads();
-    grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
-
-    const int nb = n >> 5, mb = m >> 5;
-    const int G = gridDim.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int *abort_flag = &sh->abort_flag;
-
-    if (warp == kConsumerWarps) {
-        // ------------------------------- producer warp ---------------------------------------------
-        // reads only the packed codes (weights), so it does not wait for the previous kernel
-        if (lane == 0) {
-            uint32_t s = 0, round = 0;  // ring slot, number of times the ring wrapped
-            SegmentIter segs(mode, mb, nb, G, blockIdx.x);
-            long seg0, seg1;
-            while (segs.next(seg0, seg1)) {
-                const uint8_t *src = codes + (size_t)seg0 * kBlockBytes;
-                for (int left = (int)(seg1 - seg0); left > 0 && !*abort_flag; left -= kStageBlocks) {
-                    const uint32_t bytes = (uint32_t)min(kStageBlocks, left) * kBlockBytes;
-                    if (round > 0) mbar_wait(smem_u32(&sh->empty[s]), (round - 1) & 1, abort_flag, status, 1);
-                    const uint32_t bar = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(bar, bytes);
-                    bulk_g2s(ring + s * kStageBytes, src, bytes, bar);
-                    src += kStageBytes;
-                    if (++s == (uint32_t)nstages) { s = 0; round++; }
-                }
-            }
-        }
-        return;  // every copy issued above is waited for by the consumer warps below
-    }
-
-    // ------------------------------------ consumer warps ------------------------------------------------
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
     // flips the sign of the first (low) half of the pair
-    for (int i = threadIdx.x; i < 1024 * 8; i += kConsumerThreads) {
+    for (int i = threadIdx.x; i < 1024 * 8; i += kThreads) {
         const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
         reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
     }
-    consumer_sync();
-    grid_dependency_wait();  // x, out and the workspace belong to the stream's data flow
+    grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
+    grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
+    if constexpr (XS) {
+        // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(x);
+        const int words = bs * (n >> 1);
+        for (int i = threadIdx.x; i < words; i += kThreads) {
+            const int blk = i >> 4, w = i & 15;          // 16 words per 32-column block
+            reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = __ldg(xw + i);
+        }
+    }
+    __syncthreads();
 
+    volatile int *abort_flag = &sh->abort_flag;
     const int g = lane >> 2, t = lane & 3;
-    const bool xvalid = g < bs;
-    const uint32_t *xrow = reinterpret_cast<const uint32_t *>(x + (size_t)(xvalid ? g : 0) * n + 2 * t);
+    const int xg = g < bs ? g : 0;  // lanes of unused batch columns alias row 0; their results are never stored
+    const uint32_t *xrow = reinterpret_cast<const uint32_t *>(x + (size_t)xg * n + 2 * t);
+    const uint4 *xsrow = xs + (size_t)xg * nb * 4 + t;
     const uint32_t lut_lane = smem_u32(lut) + lane * 4;
     const uint32_t own_off = lane * (4 * K), nxt_off = ((lane + 1) & 31) * (4 * K);
     const uint32_t off0 = warp * kBlockBytes, off1 = (warp + kConsumerWarps) * kBlockBytes;
 
-    uint32_t s = 0, phase = 0;  // ring slot and the parity its "full" barrier completes next
+    uint32_t s = 0, phase = 0, segno = 0;  // ring slot, parity its "full" barrier completes next
     SegmentIter segs(mode, mb, nb, G, blockIdx.x);
     long seg0, seg1;
     while (segs.next(seg0, seg1)) {
         const int M = (int)(seg0 / nb);
         float acc[2][4] = {};
-        // this warp's first block of the stage, as 32-column index inside the row block
-        const uint32_t *xp = xrow + 16 * ((int)(seg0 - (long)M * nb) + warp);
-        for (int left = (int)(seg1 - seg0); left > 0; left -= kStageBlocks) {
+        int N0 = (int)(seg0 - (long)M * nb) + warp;  // this warp's first block of the stage inside the row block
+        for (int left = (int)(seg1 - seg0); left > 0; left -= kStageBlocks, N0 += kStageBlocks) {
             const bool v0 = warp < left, v1 = warp + kConsumerWarps < left;
-            // x fragments do not depend on the stage: issue them before waiting
-            uint32_t xb0[4] = {0u, 0u, 0u, 0u}, xb1[4] = {0u, 0u, 0u, 0u};  // [ks][cols 2t,2t+1 | cols 2t+8,2t+9]
-            if (xvalid) {
-                if (v0) { xb0[0] = __ldg(xp); xb0[1] = __ldg(xp + 4); xb0[2] = __ldg(xp + 8); xb0[3] = __ldg(xp + 12); }
-                const uint32_t *xq = xp + 16 * kConsumerWarps;
-                if (v1) { xb1[0] = __ldg(xq); xb1[1] = __ldg(xq + 4); xb1[2] = __ldg(xq + 8); xb1[3] = __ldg(xq + 12); }
-            }
-            xp += 16 * kStageBlocks;
-            mbar_wait(smem_u32(&sh->full[s]), phase, abort_flag, status, 2);
-            const uint32_t stage = ring + s * kStageBytes;
-            LaneCodes<K> own0 = {}, nxt0 = {}, own1 = {}, nxt1 = {};
+            LaneCodes<K> own0, nxt0, own1, nxt1;
+            uint32_t xb0[4], xb1[4];  // [ks][cols 2t,2t+1 | cols 2t+8,2t+9]
             if (v0) {
+                if constexpr (XS) {
+                    const uint4 a = xsrow[N0 * 4];
+                    xb0[0] = a.x; xb0[1] = a.y; xb0[2] = a.z; xb0[3] = a.w;
+                    if (v1) { const uint4 b = xsrow[(N0 + kConsumerWarps) * 4]; xb1[0] = b.x; xb1[1] = b.y; xb1[2] = b.z; xb1[3] = b.w; }
+                } else {
+                    const uint32_t *xp = xrow + 16 * N0;
+                    xb0[0] = __ldg(xp); xb0[1] = __ldg(xp + 4); xb0[2] = __ldg(xp + 8); xb0[3] = __ldg(xp + 12);
+                    if (v1) {
+                        xp += 16 * kConsumerWarps;
+                        xb1[0] = __ldg(xp); xb1[1] = __ldg(xp + 4); xb1[2] = __ldg(xp + 8); xb1[3] = __ldg(xp + 12);
+                    }
+                }
+                mbar_wait(smem_u32(&sh->full[s]), phase, abort_flag, status, 2);
+                const uint32_t stage = ring + s * kStageBytes;
                 own0 = lds_lane_codes<K>(stage + off0 + own_off);
                 nxt0 = lds_lane_codes<K>(stage + off0 + nxt_off);
+                if (v1) {
+                    own1 = lds_lane_codes<K>(stage + off1 + own_off);
+                    nxt1 = lds_lane_codes<K>(stage + off1 + nxt_off);
+                }
             }
-            if (v1) {
-                own1 = lds_lane_codes<K>(stage + off1 + own_off);
-                nxt1 = lds_lane_codes<K>(stage + off1 + nxt_off);
-            }
-            // the stage's bytes are in registers: hand it back to the producer before decoding
+            // the warp's bytes of this stage are in registers: release the slot before decoding
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
             if (++s == (uint32_t)nstages) { s = 0; phase ^= 1; }
-            if (v0) decode_block<K>(own0, nxt0, xb0, acc, lut_lane);
-            if (v1) decode_block<K>(own1, nxt1, xb1, acc, lut_lane);
+            if (v0) {
+                decode_block<K>(own0, nxt0, xb0, acc, lut_lane);
+                if (v1) decode_block<K>(own1, nxt1, xb1, acc, lut_lane);
+            }
+            if (threadIdx.x == 0) produce_stage<K>(sh, codes, ring, nstages, mode, nb, status);
         }
-        finish_segment<kConsumerWarps>(acc, red, sh, out, partial, counters, M, nb, (long)mb * nb, G, kmax, m, bs,
-                                       mode == kModeRows);
+        finish_segment<kConsumerWarps>(acc, DB ? red + (segno & 1) * red_floats : red, sh, out, partial, counters, M, nb,
+                                       (long)mb * nb, G, kmax, m, bs, mode == kModeRows, !DB);
+        segno++;
     }
     if (*abort_flag) {
         // a wait gave up: give copies that may still be in flight time to land before the CTA retires
@@ -522,21 +558,15 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
     return QTIP_OK;
 }
 
-template <int K>
-int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
-               uint8_t *workspace, cudaStream_t s) {
-    constexpr int kStageBytes = kStageBlocks * 128 * K;
-    // the ring gets whatever the table and the reduction buffer leave: 2 to 4 stages of 15.5 KiB * K/2
-    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
-    int nstages = (kSmemLimit - kCtrlBytes - kLutBytes - red_bytes) / kStageBytes;
-    if (nstages > kMaxStages) nstages = kMaxStages;
-    if (nstages < 2) return QTIP_ERR_BAD_ARG;
-    const int smem_total = kCtrlBytes + kLutBytes + nstages * kStageBytes + red_bytes;
+template <int K, bool XS, bool DB>
+int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
+                       uint8_t *workspace, int nstages, int smem_total, cudaStream_t s) {
     static bool attr_set[64] = {};
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kSmemLimit));
         attr_set[dev] = true;
     }
     const Partition p = make_partition(m, n, K);
@@ -550,9 +580,31 @@ int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode, nstages,
-                                     workspace));
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode,
+                                     nstages, workspace));
     return check_launch();
+}
+
+template <int K>
+int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
+               uint8_t *workspace, cudaStream_t s) {
+    constexpr int kStageBytes = kStageBlocks * 128 * K;
+    // shared memory: control + table are fixed; the ring gets what the reduction buffer(s) and the
+    // staged x leave.  Prefer (double-buffered reduction, x in shared memory) while >= 3 stages remain.
+    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
+    const int x_bytes = bs * n * 2;
+    const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
+    const bool db = bs <= 2;
+    const int fixed = (db ? 2 : 1) * red_bytes;
+    const bool xs = (avail - fixed - x_bytes) / kStageBytes >= 3;
+    int nstages = (avail - fixed - (xs ? x_bytes : 0)) / kStageBytes;
+    if (nstages > kMaxStages) nstages = kMaxStages;
+    if (nstages < 2) return QTIP_ERR_BAD_ARG;
+    const int smem_total = kCtrlBytes + kLutBytes + nstages * kStageBytes + fixed + (xs ? x_bytes : 0);
+    if (xs && db) return launch_hyb_variant<K, true, true>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
+    if (xs) return launch_hyb_variant<K, true, false>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
+    if (db) return launch_hyb_variant<K, false, true>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
+    return launch_hyb_variant<K, false, false>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
 }
 
 }  // namespace
