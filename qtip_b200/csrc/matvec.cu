@@ -2,20 +2,27 @@
 //
 // Partition.  The packed matrix is a sequence of B = (m/32)*(n/32) blocks (a block is a 2x2 group of
 // 16x16 tiles, 128*K contiguous bytes; the blocks of one 32-row block are contiguous).  The grid
-// has at most one CTA per SM.  Two schedules exist and the host picks the cheaper one per shape:
+// has at most one CTA (32 warps) per SM.  Two schedules exist and the host picks the cheaper one:
 //   rows     CTA c owns whole 32-row blocks c, c+G, ...: no cross-CTA reduction at all;
 //   stream-K CTA c owns the contiguous block range [c*B/G, (c+1)*B/G), cut into segments at
 //            row-block boundaries: perfectly balanced bytes, but row blocks shared by several
 //            CTAs need the ticket reduction below.
 //
-// Data path.  A producer warp streams the CTA's segments through a ring of shared-memory stages
-// with cp.async.bulk (TMA, completion on an mbarrier per stage), running ahead of the consumers
-// across segment boundaries.  31 consumer warps take the blocks of a stage two at a time: a lane
-// reads its 4K contiguous bytes and those of lane+1 (wrap-around bits) from the stage, decodes 16
-// trellis states into four mma.m16n8k16 A fragments in registers - HYB: h = s*(s+1), entry
-// (h>>6)&1023 of a 1024-entry table (the 512-entry LUT and its sign-flipped twin) kept as 32
-// lane-private copies in shared memory, so gathers never conflict - and multiplies them with x held in the B fragment (column j of B = batch row
-// j, so up to 8 batch rows ride along for free).  fp32 accumulation in the MMA.
+// Data path.  Inside a segment warp w takes blocks w, w+32, ...  A lane pulls its 4K contiguous
+// bytes of a block with one streaming (L1-bypassing) 64/96/128-bit load straight into registers;
+// each warp keeps D such loads in flight (software pipeline across its blocks and across segment
+// boundaries), which is 32 KiB in flight per SM.  The wrap-around bits of the tail-biting stream
+// come from lane+1 by shuffle.  A lane decodes its 16 trellis states into four mma.m16n8k16 A
+// fragments in registers - HYB: h = s*(s+1), entry (h>>6)&1023 of a 1024-entry table (the 512-entry
+// LUT and its sign-flipped twin) kept as 32 lane-private copies in shared memory, so gathers never
+// conflict - and multiplies them with x held in the B fragment (column j of B = batch row j, so up
+// to 8 batch rows ride along for free).  fp32 accumulation in the MMA.  x is staged once per CTA
+// in shared memory in fragment order (one 16-byte load per block and lane).
+//
+// The kernel is instruction-issue bound, not HBM bound (about 5 instructions per state are
+// irreducible: shift, multiply-add hash, mask, multiply-add address, shared load), so the loop
+// carries no barriers: an earlier variant that staged the codes through a cp.async.bulk ring with
+// mbarriers spent 74 of 158 instructions per block on ring control and ran 35 % slower.
 //
 // Reduction.  Warps of a CTA are summed through shared memory at the end of a segment.  When a
 // row block is shared by several CTAs each stores its partial sums to the workspace and takes a
@@ -23,13 +30,9 @@
 // so the output is deterministic and is overwritten, never accumulated into.
 //
 // Launch overlap.  The kernel is launched with programmatic stream serialization: everything that
-// touches only weights (barrier setup, LUT replication, the first ring fills) runs before
-// griddepcontrol.wait, i.e. while the previous kernel of the stream drains; x, out and the
-// workspace are touched only after it.
-//
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records an error code in
-// the workspace status word, raises a CTA-wide abort flag that makes all later waits fall through,
-// and the kernel runs to its end (with meaningless results) instead of hanging.
+// touches only weights (the first code loads, the table build) runs before griddepcontrol.wait,
+// i.e. while the previous kernel of the stream drains; x, out and the workspace are touched only
+// after it.  The kernel contains no spin-waits.
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
 #include <cstdlib>
@@ -39,26 +42,21 @@
 namespace qtip {
 namespace {
 
-constexpr int kConsumerWarps = 32;               // all 32 warps decode; lane 0 of warp 0 also feeds the ring
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = 1024;
-constexpr int kStageBlocks = 2 * kConsumerWarps; // blocks per ring stage: two per warp
+constexpr int kConsumerWarps = 32;
+constexpr int kThreads = kConsumerWarps * 32;
 // Gather table: 1024 entries (sign bit of the hash folded in as the top index bit, so no separate
 // sign flip is needed) x 32 lane-private copies x half2 = 128 KiB.  Entry e, copy l at byte e*128 + l*4:
 // every lane reads its own bank, so a warp's 32 random lookups never conflict.
 constexpr int kLutBytes = 1024 * 32 * 4;
 constexpr int kCtrlBytes = 256;
 constexpr int kSmemLimit = 227 * 1024;
-constexpr int kMaxStages = 8;
 constexpr int kMaxBatch = 8;
-constexpr unsigned kSpinLimit = 1u << 22;        // polls of ~20-40 ns each: gives up after ~0.1 s
 
 // ---- workspace layout (all offsets fixed, independent of the problem) -----------------------------
 // [0, 64 KiB)   ticket counters, one uint32 per 32-row block (m <= 524288); zero between calls
-// [64 KiB, +256) status word (0 = ok) and padding
+// [64 KiB, +256) reserved
 // [.., end)     partial sums: [row block][contributor][8 batch x 32 rows] fp32
 constexpr size_t kCounterBytes = 64 * 1024;
-constexpr size_t kStatusOffset = kCounterBytes;
 constexpr size_t kPartialOffset = kCounterBytes + 256;
 constexpr int kMaxGrid = 1024;  // sizing bound for the number of CTAs
 
@@ -98,63 +96,8 @@ Partition make_partition(int m, int n, int K) {
 // ---- PTX wrappers -----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  `abort_flag` lives in shared memory; once set every wait returns immediately.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned *status, int code) {
-    if (mbar_try_wait(bar, parity)) return;
-    for (unsigned spin = 0; spin < kSpinLimit; spin++) {
-        if (mbar_try_wait(bar, parity)) return;
-        if (*abort_flag) return;
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0u, (unsigned)code);
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-// A lane's 4K bytes of a block staged in shared memory.
-template <int K>
-__device__ __forceinline__ LaneCodes<K> lds_lane_codes(uint32_t addr) {
-    LaneCodes<K> c;
-    if constexpr (K == 2) {
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(c.w[0]), "=r"(c.w[1]) : "r"(addr) : "memory");
-    } else if constexpr (K == 3) {
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(c.w[0]) : "r"(addr) : "memory");
-        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(c.w[1]) : "r"(addr) : "memory");
-        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(c.w[2]) : "r"(addr) : "memory");
-    } else {
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(c.w[0]), "=r"(c.w[1]), "=r"(c.w[2]), "=r"(c.w[3])
-                     : "r"(addr)
-                     : "memory");
-    }
-    return c;
-}
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -184,13 +127,7 @@ struct SegmentIter {
 };
 
 struct Shared {            // control block at the start of dynamic shared memory
-    unsigned long long full[kMaxStages];
-    unsigned long long empty[kMaxStages];
-    int abort_flag;
     int is_last;
-    // cursor of the ring producer (touched by thread 0 only)
-    long p_pos, p_end, p_step, p_seg_end;   // next block to fetch; end of the CTA's work; rows-mode stride; end of the current segment
-    unsigned p_slot, p_round;
 };
 static_assert(sizeof(Shared) <= kCtrlBytes, "control block too large");
 
@@ -317,76 +254,62 @@ __device__ __forceinline__ void decode_block(const LaneCodes<K> &own, const Lane
     }
 }
 
-// Ring producer step (thread 0 only): fetch the next stage of this CTA's work, if any, into ring slot
-// p_slot.  A slot may be refilled once all 32 warps have pulled their bytes of its previous use.
+// Next lane's codes (wrap-around bits of the tail-biting stream: lane 31 takes lane 0's).
 template <int K>
-__device__ __forceinline__ void produce_stage(Shared *sh, const uint8_t *__restrict__ codes, uint32_t ring, int nstages,
-                                              int mode, long nb, unsigned *status) {
-    constexpr int kBlockBytes = 128 * K;
-    constexpr int kStageBytes = kStageBlocks * kBlockBytes;
-    long pos = sh->p_pos;
-    if (pos >= sh->p_end) return;
-    volatile int *abort_flag = &sh->abort_flag;
-    if (*abort_flag) return;
-    long seg_end = sh->p_seg_end;
-    if (pos >= seg_end) {  // open the next segment
-        if (mode == kModeRows) { pos += sh->p_step - nb; seg_end = pos + nb; if (pos >= sh->p_end) { sh->p_pos = pos; return; } }
-        else seg_end = min(sh->p_end, (pos / nb + 1) * nb);
-        sh->p_seg_end = seg_end;
-    }
-    const unsigned slot = sh->p_slot, round = sh->p_round;
-    if (round > 0) mbar_wait(smem_u32(&sh->empty[slot]), (round - 1) & 1, abort_flag, status, 1);
-    const uint32_t bytes = (uint32_t)min((long)kStageBlocks, seg_end - pos) * kBlockBytes;
-    const uint32_t bar = smem_u32(&sh->full[slot]);
-    mbar_expect_tx(bar, bytes);
-    bulk_g2s(ring + slot * kStageBytes, codes + (size_t)pos * kBlockBytes, bytes, bar);
-    sh->p_pos = pos + min((long)kStageBlocks, seg_end - pos);
-    if (slot + 1 == (unsigned)nstages) { sh->p_slot = 0; sh->p_round = round + 1; }
-    else sh->p_slot = slot + 1;
+__device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, int lane) {
+    LaneCodes<K> o;
+#pragma unroll
+    for (int i = 0; i < K; i++) o.w[i] = __shfl_sync(kFullMask, c.w[i], lane + 1);
+    return o;
 }
 
 // XS: x is staged once per CTA in shared memory, permuted so that a lane's four B-fragment words of
 // a block are one 16-byte load; otherwise they are read from global memory (L1-resident) per block.
 // DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
-template <int K, bool XS, bool DB>
+// D:  software-pipeline depth - each warp keeps D of its blocks' codes in flight in registers.
+template <int K, bool XS, bool DB, int D>
 __global__ void __launch_bounds__(kThreads, 1)
     matvec_hyb_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
-                      const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int mode, int nstages,
+                      const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int mode,
                       uint8_t *__restrict__ workspace) {
     constexpr int kBlockBytes = 128 * K;
-    constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: control block | LUT | ring stages | reduction buffer(s) [32][bs][32] fp32 | x (bs, n) fp16 permuted
+    // layout: control block | LUT | reduction buffer(s) [32][bs][32] fp32 | x (bs, n) fp16 permuted
     Shared *sh = reinterpret_cast<Shared *>(smem);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kCtrlBytes);
-    const uint32_t ring = smem_u32(smem + kCtrlBytes + kLutBytes);
     const int red_floats = kConsumerWarps * 32 * bs;
-    float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes + nstages * kStageBytes);
+    float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes);
     uint4 *xs = reinterpret_cast<uint4 *>(red + (DB ? 2 : 1) * red_floats);
 
     unsigned *counters = reinterpret_cast<unsigned *>(workspace);
-    unsigned *status = reinterpret_cast<unsigned *>(workspace + kStatusOffset);
     float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
 
     const int nb = n >> 5, mb = m >> 5;
     const int G = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint8_t *lane_codes = codes + lane * (4 * K);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < nstages; s++) {
-            mbar_init(smem_u32(&sh->full[s]), 1);
-            mbar_init(smem_u32(&sh->empty[s]), kConsumerWarps);
+    // Segment bookkeeping in 32-bit block indices (B = mb*nb < 2^31 is checked by the host).
+    // rows mode: segments are whole row blocks c, c+G, ...; stream-K: [r0, r1) cut at row boundaries.
+    const int B = mb * nb;
+    int pos, end;
+    if (mode == kModeRows) { pos = blockIdx.x * nb; end = B; }
+    else { pos = (int)range_start(blockIdx.x, B, G); end = (int)range_start(blockIdx.x + 1, B, G); }
+    auto seg_end_of = [&](int p) { return mode == kModeRows ? p + nb : min(end, (p / nb + 1) * nb); };
+    auto next_seg = [&](int e) { return mode == kModeRows ? e + (G - 1) * nb : e; };
+
+    // First loads of this warp: packed codes are weights, so they are issued before the table build
+    // and before waiting for the previous kernel of the stream.
+    LaneCodes<K> buf[D];
+    int seg_end = seg_end_of(pos);
+    {
+#pragma unroll
+        for (int d = 0; d < D; d++) {
+            const int b = pos + warp + d * kConsumerWarps;
+            if (b < seg_end) buf[d] = load_lane_codes<K>(lane_codes + (size_t)b * kBlockBytes);
         }
-        sh->abort_flag = 0;
-        sh->is_last = 0;
-        SegmentIter it(mode, mb, nb, G, blockIdx.x);
-        sh->p_pos = it.pos; sh->p_end = it.end; sh->p_step = it.step;
-        sh->p_seg_end = mode == kModeRows ? it.pos + nb : min(it.end, (it.pos / nb + 1) * nb);
-        sh->p_slot = 0; sh->p_round = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // fill the ring: packed codes are weights, no need to wait for the previous kernel
-        for (int s = 0; s < nstages; s++) produce_stage<K>(sh, codes, ring, nstages, mode, nb, status);
     }
+    if (threadIdx.x == 0) sh->is_last = 0;
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
     // flips the sign of the first (low) half of the pair
     for (int i = threadIdx.x; i < 1024 * 8; i += kThreads) {
@@ -406,65 +329,66 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncthreads();
 
-    volatile int *abort_flag = &sh->abort_flag;
     const int g = lane >> 2, t = lane & 3;
     const int xg = g < bs ? g : 0;  // lanes of unused batch columns alias row 0; their results are never stored
     const uint32_t *xrow = reinterpret_cast<const uint32_t *>(x + (size_t)xg * n + 2 * t);
     const uint4 *xsrow = xs + (size_t)xg * nb * 4 + t;
     const uint32_t lut_lane = smem_u32(lut) + lane * 4;
-    const uint32_t own_off = lane * (4 * K), nxt_off = ((lane + 1) & 31) * (4 * K);
-    const uint32_t off0 = warp * kBlockBytes, off1 = (warp + kConsumerWarps) * kBlockBytes;
 
-    uint32_t s = 0, phase = 0, segno = 0;  // ring slot, parity its "full" barrier completes next
-    SegmentIter segs(mode, mb, nb, G, blockIdx.x);
-    long seg0, seg1;
-    while (segs.next(seg0, seg1)) {
-        const int M = (int)(seg0 / nb);
+    uint32_t segno = 0;
+    while (pos < end) {
+        const int M = pos / nb;
+        const int first = pos - M * nb + warp;      // this warp's first block inside the row block
+        const int count = seg_end - pos;            // blocks in the segment
         float acc[2][4] = {};
-        int N0 = (int)(seg0 - (long)M * nb) + warp;  // this warp's first block of the stage inside the row block
-        for (int left = (int)(seg1 - seg0); left > 0; left -= kStageBlocks, N0 += kStageBlocks) {
-            const bool v0 = warp < left, v1 = warp + kConsumerWarps < left;
-            LaneCodes<K> own0, nxt0, own1, nxt1;
-            uint32_t xb0[4], xb1[4];  // [ks][cols 2t,2t+1 | cols 2t+8,2t+9]
-            if (v0) {
-                if constexpr (XS) {
-                    const uint4 a = xsrow[N0 * 4];
-                    xb0[0] = a.x; xb0[1] = a.y; xb0[2] = a.z; xb0[3] = a.w;
-                    if (v1) { const uint4 b = xsrow[(N0 + kConsumerWarps) * 4]; xb1[0] = b.x; xb1[1] = b.y; xb1[2] = b.z; xb1[3] = b.w; }
-                } else {
-                    const uint32_t *xp = xrow + 16 * N0;
-                    xb0[0] = __ldg(xp); xb0[1] = __ldg(xp + 4); xb0[2] = __ldg(xp + 8); xb0[3] = __ldg(xp + 12);
-                    if (v1) {
-                        xp += 16 * kConsumerWarps;
-                        xb1[0] = __ldg(xp); xb1[1] = __ldg(xp + 4); xb1[2] = __ldg(xp + 8); xb1[3] = __ldg(xp + 12);
-                    }
-                }
-                mbar_wait(smem_u32(&sh->full[s]), phase, abort_flag, status, 2);
-                const uint32_t stage = ring + s * kStageBytes;
-                own0 = lds_lane_codes<K>(stage + off0 + own_off);
-                nxt0 = lds_lane_codes<K>(stage + off0 + nxt_off);
-                if (v1) {
-                    own1 = lds_lane_codes<K>(stage + off1 + own_off);
-                    nxt1 = lds_lane_codes<K>(stage + off1 + nxt_off);
-                }
+        // warp handles blocks first, first+32, ... ; buf[d] holds block i*... in round-robin order
+        const uint8_t *src = lane_codes + (size_t)(pos + warp) * kBlockBytes;
+        int i = warp;
+        for (; i + (D - 1) * kConsumerWarps < count; i += D * kConsumerWarps) {
+            // all D buffered blocks are valid in this trip
+#pragma unroll
+            for (int d = 0; d < D; d++) {
+                const LaneCodes<K> own = buf[d];
+                const int nxt_i = i + (d + D) * kConsumerWarps;
+                if (nxt_i < count) buf[d] = load_lane_codes<K>(src + (size_t)(d + D) * kConsumerWarps * kBlockBytes);
+                const LaneCodes<K> nxt = next_lane_codes<K>(own, lane);
+                uint32_t xb[4];
+                const int N = first + (i - warp) + d * kConsumerWarps;
+                if constexpr (XS) { const uint4 a = xsrow[N * 4]; xb[0] = a.x; xb[1] = a.y; xb[2] = a.z; xb[3] = a.w; }
+                else { const uint32_t *xp = xrow + 16 * N; xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12); }
+                decode_block<K>(own, nxt, xb, acc, lut_lane);
             }
-            // the warp's bytes of this stage are in registers: release the slot before decoding
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
-            if (++s == (uint32_t)nstages) { s = 0; phase ^= 1; }
-            if (v0) {
-                decode_block<K>(own0, nxt0, xb0, acc, lut_lane);
-                if (v1) decode_block<K>(own1, nxt1, xb1, acc, lut_lane);
+            src += (size_t)D * kConsumerWarps * kBlockBytes;
+        }
+        // tail: fewer than D blocks left for this warp (no further loads in this segment)
+#pragma unroll
+        for (int d = 0; d < D; d++) {
+            if (i + d * kConsumerWarps < count) {
+                const LaneCodes<K> own = buf[d];
+                const LaneCodes<K> nxt = next_lane_codes<K>(own, lane);
+                uint32_t xb[4];
+                const int N = first + (i - warp) + d * kConsumerWarps;
+                if constexpr (XS) { const uint4 a = xsrow[N * 4]; xb[0] = a.x; xb[1] = a.y; xb[2] = a.z; xb[3] = a.w; }
+                else { const uint32_t *xp = xrow + 16 * N; xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12); }
+                decode_block<K>(own, nxt, xb, acc, lut_lane);
             }
-            if (threadIdx.x == 0) produce_stage<K>(sh, codes, ring, nstages, mode, nb, status);
+        }
+        // next segment: start its first loads before the CTA-wide reduction of this one
+        const int npos = next_seg(seg_end);
+        int nseg_end = seg_end;
+        if (npos < end) {
+            nseg_end = seg_end_of(npos);
+#pragma unroll
+            for (int d = 0; d < D; d++) {
+                const int b = npos + warp + d * kConsumerWarps;
+                if (b < nseg_end) buf[d] = load_lane_codes<K>(lane_codes + (size_t)b * kBlockBytes);
+            }
         }
         finish_segment<kConsumerWarps>(acc, DB ? red + (segno & 1) * red_floats : red, sh, out, partial, counters, M, nb,
-                                       (long)mb * nb, G, kmax, m, bs, mode == kModeRows, !DB);
+                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB);
         segno++;
-    }
-    if (*abort_flag) {
-        // a wait gave up: give copies that may still be in flight time to land before the CTA retires
-        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        pos = npos;
+        seg_end = nseg_end;
     }
 }
 
@@ -553,6 +477,7 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
                  size_t workspace_bytes) {
     if (!out || !codes || !x || K < 2 || K > 4 || bs < 1 || bs > kMaxBatch) return QTIP_ERR_BAD_ARG;
     if (m <= 0 || n <= 0 || (m & 31) || (n & 31) || (size_t)(m >> 5) * 4 > kCounterBytes) return QTIP_ERR_BAD_SHAPE;
+    if ((long)(m >> 5) * (n >> 5) >= (1L << 30)) return QTIP_ERR_BAD_SHAPE;  // block indices are 32-bit
     if (!workspace || workspace_bytes < qtip_matvec_workspace_bytes(m, n, bs)) return QTIP_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(codes, 16) || !aligned(x, 4) || !aligned(out, 4)) return QTIP_ERR_ALIGNMENT;
     return QTIP_OK;
@@ -560,12 +485,13 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
 
 template <int K, bool XS, bool DB>
 int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
-                       uint8_t *workspace, int nstages, int smem_total, cudaStream_t s) {
+                       uint8_t *workspace, int smem_total, cudaStream_t s) {
+    constexpr int D = K == 2 ? 4 : 2;  // blocks in flight per warp: 32 warps x D x 128K bytes = 32 KiB per SM
     static bool attr_set[64] = {};
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kSmemLimit));
         attr_set[dev] = true;
     }
@@ -580,31 +506,26 @@ int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode,
-                                     nstages, workspace));
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode,
+                                     workspace));
     return check_launch();
 }
 
 template <int K>
 int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
                uint8_t *workspace, cudaStream_t s) {
-    constexpr int kStageBytes = kStageBlocks * 128 * K;
-    // shared memory: control + table are fixed; the ring gets what the reduction buffer(s) and the
-    // staged x leave.  Prefer (double-buffered reduction, x in shared memory) while >= 3 stages remain.
+    // shared memory: control + table are fixed; then the reduction buffer(s) and, when it fits, x
     const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
     const int x_bytes = bs * n * 2;
     const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
-    const bool db = bs <= 2;
+    const bool db = 2 * red_bytes <= avail / 2;
     const int fixed = (db ? 2 : 1) * red_bytes;
-    const bool xs = (avail - fixed - x_bytes) / kStageBytes >= 3;
-    int nstages = (avail - fixed - (xs ? x_bytes : 0)) / kStageBytes;
-    if (nstages > kMaxStages) nstages = kMaxStages;
-    if (nstages < 2) return QTIP_ERR_BAD_ARG;
-    const int smem_total = kCtrlBytes + kLutBytes + nstages * kStageBytes + fixed + (xs ? x_bytes : 0);
-    if (xs && db) return launch_hyb_variant<K, true, true>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
-    if (xs) return launch_hyb_variant<K, true, false>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
-    if (db) return launch_hyb_variant<K, false, true>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
-    return launch_hyb_variant<K, false, false>(out, codes, x, tlut, m, n, bs, workspace, nstages, smem_total, s);
+    const bool xs = fixed + x_bytes <= avail;
+    const int smem_total = kCtrlBytes + kLutBytes + fixed + (xs ? x_bytes : 0);
+    if (xs && db) return launch_hyb_variant<K, true, true>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
+    if (xs) return launch_hyb_variant<K, true, false>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
+    if (db) return launch_hyb_variant<K, false, true>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
+    return launch_hyb_variant<K, false, false>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
 }
 
 }  // namespace

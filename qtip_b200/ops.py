@@ -112,12 +112,6 @@ def matvec_workspace(m, n, bs, device):
     return ws
 
 
-def matvec_status(workspace):
-    """Status word the fused matvec leaves in its workspace: 0 = ok, 1 / 2 = a bounded wait on a ring
-    barrier (producer / consumer side) gave up, 3 = shared-memory carve overflow.  Synchronises."""
-    return int(workspace[65536:65540].view(torch.int32).item())
-
-
 # ---------------------------------------------------------------------------------------------
 # ops
 # ---------------------------------------------------------------------------------------------

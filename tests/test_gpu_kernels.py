@@ -101,7 +101,6 @@ def test_matvec_hyb(K, m, n, bs):
     assert rel_l2(y.cpu().numpy(), want) < 2e-6  # fp32 accumulation of exact fp16 products: only summation order differs
     y2 = ops.decompress_matvec(dev(lay["codes"]), dev(lay["x"]), dev(lay["tlut"]), K, m, n)
     assert torch.equal(y, y2), "result must be deterministic run to run"
-    assert ops.matvec_status(ops.matvec_workspace(m, n, bs, DEV)) == 0
 
 
 def test_matvec_hyb_upstream_test_inputs():
