@@ -105,6 +105,39 @@ int qtip_rht(void *out, int out_dtype, const void *in, int in_dtype, long rows, 
              int sign_in_dtype, const float *sign_out, long n_signs, const uint32_t *hadk_bits, int kfac,
              int transpose, float scale, void *stream);
 
+/* qtip_rht with the element-wise neighbours of a QTIP linear in a decoder layer fused into the load:
+ *   v = in (+ residual)            the sum rounded to fp16, written to residual_out when given
+ *   v = RMSNorm(v) * norm_weight   LlamaRMSNorm, model/llama.py:129-136 (fp32 statistics, fp16 product)
+ *   v = silu(gate) * v             the SwiGLU product of LlamaMLP.forward, model/llama.py:399-400
+ * then sign_in, Hadamard, scale, sign_out as qtip_rht.  residual, residual_out, norm_weight and gate
+ * are fp16 and optional (NULL); residual and gate use the row layout of `in`.
+ * in_row_stride: elements between consecutive input rows, 0 = all rows read the same input row
+ * (one launch transforms one activation with several sign vectors - q/k/v or gate/up - with
+ * n_signs = rows*n).  out and residual_out must not alias any input. */
+int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long rows, long in_row_stride, int n,
+                   const void *residual, void *residual_out, const void *norm_weight, float eps, const void *gate,
+                   const void *sign_in, int sign_in_dtype, const float *sign_out, long n_signs,
+                   const uint32_t *hadk_bits, int kfac, int transpose, float scale, void *stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Decode-loop support (batch 1): the per-token attention pieces between the QTIP linears, so that a
+ * decode step is one CUDA graph of this library's launches.  fp16 tensors; `pos` points to the
+ * token position in device memory (read at run time, so a captured graph can be replayed).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Rotary embedding of q (n_heads, head_dim; in place) and k (n_kv_heads, head_dim), and append of the
+ * rotated k and of v to the caches at row *pos (caches are (max_positions, n_kv_heads*head_dim)).
+ * Replaces apply_rotary_pos_emb + StaticCache.update (model/llama.py:797-898,
+ * model/cache_utils.py:1147-1193) for a single new token. */
+int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, void *cache_v, const int *pos,
+                        int n_heads, int n_kv_heads, int head_dim, float theta, void *stream);
+
+/* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128.
+ * Replaces the scaled_dot_product_attention call of LlamaSdpaAttention.forward (model/llama.py:884-891)
+ * for a single new token. */
+int qtip_attn_decode(void *out, const void *q, const void *cache_k, const void *cache_v, const int *pos, int n_heads,
+                     int n_kv_heads, int head_dim, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

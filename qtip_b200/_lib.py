@@ -26,6 +26,10 @@ SIGNATURES = {
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
+    "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,
+                            _vp]),
+    "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }
 
 _lib = None

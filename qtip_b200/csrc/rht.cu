@@ -1,16 +1,24 @@
-// Randomized Hadamard transform with the sign flips and scales fused on both sides.
+// Randomized Hadamard transform with the sign flips and scales fused on both sides, plus the
+// element-wise work that surrounds a QTIP linear inside a decoder layer.
 //
 // One row of n = kfac * 2^p values is transformed entirely in shared memory:
-//   1. load, multiply by sign_in;
+//   0. optional prologue, all fused into the load:  v = in (+ residual) ; residual_out = v ;
+//      v = RMSNorm(v) * norm_weight ; v = silu(gate) * v
+//   1. multiply by sign_in;
 //   2. Walsh-Hadamard over the 2^p-long segments: radix-16 passes over shared memory
 //      (4 butterfly stages per pass in registers);
 //   3. kfac > 1: multiply the (kfac, 2^p) view from the left by the +-1 matrix hadK.  This is the
 //      only super-linear part (kfac^2 * 2^p adds), so it is spread over several CTAs: CTA (i, r) of
-//      the grid repeats steps 1-2 for row r (cheap, data comes from L2) and produces kRowsPerCta
+//      the grid repeats steps 0-2 for row r (cheap, data comes from L2) and produces kRowsPerCta
 //      output rows of the (kfac, 2^p) view;
 //   4. scale, multiply by sign_out, store as fp16 or fp32.
 // Replaces hadamard::hadamard + the hadK matmul + the element-wise kernels of
-// lib/utils/matmul_had.py:105-119 and lib/codebook/bitshift.py:428-441, 465-471 upstream.
+// lib/utils/matmul_had.py:105-119 and lib/codebook/bitshift.py:428-441, 465-471 upstream; the
+// prologue options replace the residual add, LlamaRMSNorm (model/llama.py:129-136) and the
+// SwiGLU product (model/llama.py:399-400) kernels that would otherwise run in between.
+//
+// Launched with programmatic stream serialization: the hadK sign table (weights) is expanded
+// before griddepcontrol.wait, activations are touched after it.
 #include "common.cuh"
 
 namespace qtip {
@@ -18,6 +26,15 @@ namespace {
 
 constexpr int kRhtThreads = 512;
 constexpr int kRowsPerCta = 16;  // hadK output rows per CTA
+
+struct RhtArgs {
+    void *out; const void *in; const void *sign_in; const float *sign_out; const uint32_t *hadk_bits;
+    const __half *residual; __half *residual_out; const __half *norm_weight; const __half *gate;
+    long in_row_stride;  // elements between input rows (0 = every row reads the same input)
+    int out_dtype, in_dtype, sign_in_dtype;
+    int n, p, sign_rep, kfac, transpose;
+    float scale, eps;
+};
 
 template <int R>
 __device__ __forceinline__ void butterfly_pass(float *v, int n, int b) {
@@ -49,22 +66,28 @@ __device__ __forceinline__ float load_elem(const void *p, int dtype, size_t i) {
     return dtype == QTIP_F16 ? __half2float(static_cast<const __half *>(p)[i]) : static_cast<const float *>(p)[i];
 }
 
-__global__ void __launch_bounds__(kRhtThreads)
-    rht_kernel(void *__restrict__ out, int out_dtype, const void *__restrict__ in, int in_dtype, int n, int p,
-               const void *__restrict__ sign_in, int sign_in_dtype, const float *__restrict__ sign_out, int sign_rep,
-               const uint32_t *__restrict__ hadk_bits, int kfac, int transpose, float scale) {
-    extern __shared__ __align__(16) float sm[];
-    float *v = sm;            // n values
-    float *hs = sm + n;       // kRowsPerCta x kfac signs (+-1.0f), only when kfac > 1
-    const long row = blockIdx.y;
-    const size_t sign_off = (size_t)(row % sign_rep) * n;
-    const size_t roff = (size_t)row * n;
+__device__ __forceinline__ float block_sum(float x, float *scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(kFullMask, x, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += scratch[w];
+    return t;
+}
 
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        float x = load_elem(in, in_dtype, roff + j);
-        if (sign_in) x *= load_elem(sign_in, sign_in_dtype, sign_off + j);
-        v[j] = x;
-    }
+__global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int n = a.n, kfac = a.kfac;
+    float *v = sm;                    // n values
+    float *hs = sm + n;               // kRowsPerCta x kfac signs (+-1.0f), only when kfac > 1
+    float *scratch = hs + (kfac > 1 ? kRowsPerCta * kfac : 0);  // 32 floats
+    const long row = blockIdx.y;
+    const size_t sign_off = (size_t)(row % a.sign_rep) * n;
+    const size_t in_off = (size_t)row * a.in_row_stride, out_off = (size_t)row * n;
+
     const int i0 = blockIdx.x * kRowsPerCta;
     const int rows_here = min(kRowsPerCta, kfac - i0);
     if (kfac > 1) {
@@ -72,13 +95,48 @@ __global__ void __launch_bounds__(kRhtThreads)
         for (int idx = threadIdx.x; idx < rows_here * kfac; idx += blockDim.x) {
             int il = idx / kfac, k = idx % kfac;
             // hadK[i][k], or hadK[k][i] for the transposed (input-side) transform
-            int rr = transpose ? k : (i0 + il), cc = transpose ? (i0 + il) : k;
-            uint32_t bit = (hadk_bits[rr * wpr + (cc >> 5)] >> (cc & 31)) & 1u;
+            int rr = a.transpose ? k : (i0 + il), cc = a.transpose ? (i0 + il) : k;
+            uint32_t bit = (a.hadk_bits[rr * wpr + (cc >> 5)] >> (cc & 31)) & 1u;
             hs[il * kfac + k] = bit ? 1.0f : -1.0f;
         }
     }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float x = load_elem(a.in, a.in_dtype, in_off + j);
+        if (a.residual) {
+            // the residual stream is fp16: the sum is rounded to fp16 as an fp16 add would
+            x = __half2float(__float2half_rn(x + __half2float(a.residual[in_off + j])));
+            if (a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0))
+                a.residual_out[in_off + j] = __float2half_rn(x);
+        }
+        v[j] = x;
+        ss += x * x;
+    }
+    if (a.norm_weight) {
+        // LlamaRMSNorm: fp32 statistics, normalised value rounded to fp16, then times the fp16 weight
+        const float r = rsqrtf(block_sum(ss, scratch) / (float)n + a.eps);
+        for (int j = threadIdx.x; j < n; j += blockDim.x) {
+            const __half hn = __float2half_rn(v[j] * r);
+            v[j] = __half2float(__hmul(a.norm_weight[j], hn));
+        }
+    }
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float x = v[j];
+        if (a.gate) {
+            // SwiGLU: silu(gate) in fp16 precision, product rounded to fp16 (the activations are fp16 tensors)
+            const float gt = __half2float(a.gate[in_off + j]);
+            const __half sg = __float2half_rn(gt / (1.0f + __expf(-gt)));
+            x = __half2float(__hmul(sg, __float2half_rn(x)));
+        }
+        if (a.sign_in) x *= load_elem(a.sign_in, a.sign_in_dtype, sign_off + j);
+        v[j] = x;
+    }
     __syncthreads();
 
+    const int p = a.p;
     for (int b = 0; b < p;) {
         const int r = (p - b) >= 4 ? 4 : (p - b);
         switch (r) {
@@ -92,12 +150,13 @@ __global__ void __launch_bounds__(kRhtThreads)
     }
 
     const int len = 1 << p;
+    const float scale = a.scale;
     if (kfac == 1) {
         for (int j = threadIdx.x; j < n; j += blockDim.x) {
             float y = v[j] * scale;
-            if (sign_out) y *= sign_out[sign_off + j];
-            if (out_dtype == QTIP_F16) static_cast<__half *>(out)[roff + j] = __float2half_rn(y);
-            else static_cast<float *>(out)[roff + j] = y;
+            if (a.sign_out) y *= a.sign_out[sign_off + j];
+            if (a.out_dtype == QTIP_F16) static_cast<__half *>(a.out)[out_off + j] = __float2half_rn(y);
+            else static_cast<float *>(a.out)[out_off + j] = y;
         }
         return;
     }
@@ -115,9 +174,9 @@ __global__ void __launch_bounds__(kRhtThreads)
         if (k < kfac) acc0 = fmaf(hrow[k], v[k * len + j], acc0);
         const size_t o = (size_t)(i0 + il) * len + j;
         float y = (acc0 + acc1) * scale;
-        if (sign_out) y *= sign_out[sign_off + o];
-        if (out_dtype == QTIP_F16) static_cast<__half *>(out)[roff + o] = __float2half_rn(y);
-        else static_cast<float *>(out)[roff + o] = y;
+        if (a.sign_out) y *= a.sign_out[sign_off + o];
+        if (a.out_dtype == QTIP_F16) static_cast<__half *>(a.out)[out_off + o] = __float2half_rn(y);
+        else static_cast<float *>(a.out)[out_off + o] = y;
     }
 }
 
@@ -128,14 +187,36 @@ bool valid_kfac(int k) {
     return false;
 }
 
-}  // namespace
-}  // namespace qtip
+int launch_rht(RhtArgs a, long rows, void *stream) {
+    const int len = a.n / a.kfac;
+    int p = 0;
+    while ((1 << p) < len) p++;
+    a.p = p;
+    const size_t smem = ((size_t)a.n + (a.kfac > 1 ? (size_t)kRowsPerCta * a.kfac : 0) + 32) * sizeof(float);
+    if (smem > 227 * 1024) return QTIP_ERR_BAD_SHAPE;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    QTIP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(rht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.kfac > 1 ? (a.kfac + kRowsPerCta - 1) / kRowsPerCta : 1, (unsigned)rows);
+    cfg.blockDim = dim3(kRhtThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, rht_kernel, a));
+    return check_launch();
+}
 
-using namespace qtip;
-
-extern "C" int qtip_rht(void *out, int out_dtype, const void *in, int in_dtype, long rows, int n, const void *sign_in,
-                        int sign_in_dtype, const float *sign_out, long n_signs, const uint32_t *hadk_bits, int kfac,
-                        int transpose, float scale, void *stream) {
+int check_rht(const void *out, int out_dtype, const void *in, int in_dtype, long rows, int n, const void *sign_in,
+              int sign_in_dtype, const float *sign_out, long n_signs, const uint32_t *hadk_bits, int kfac) {
     if (!out || !in || rows < 0) return QTIP_ERR_BAD_ARG;
     if ((out_dtype != QTIP_F16 && out_dtype != QTIP_F32) || (in_dtype != QTIP_F16 && in_dtype != QTIP_F32))
         return QTIP_ERR_BAD_ARG;
@@ -145,25 +226,51 @@ extern "C" int qtip_rht(void *out, int out_dtype, const void *in, int in_dtype, 
     const int len = n / kfac;
     if (len < 2 || (len & (len - 1))) return QTIP_ERR_BAD_SHAPE;
     if ((sign_in || sign_out) && (n_signs < n || n_signs % n)) return QTIP_ERR_BAD_ARG;
+    if (rows > 65535) return QTIP_ERR_BAD_SHAPE;
+    return QTIP_OK;
+}
+
+}  // namespace
+}  // namespace qtip
+
+using namespace qtip;
+
+extern "C" int qtip_rht(void *out, int out_dtype, const void *in, int in_dtype, long rows, int n, const void *sign_in,
+                        int sign_in_dtype, const float *sign_out, long n_signs, const uint32_t *hadk_bits, int kfac,
+                        int transpose, float scale, void *stream) {
+    int st = check_rht(out, out_dtype, in, in_dtype, rows, n, sign_in, sign_in_dtype, sign_out, n_signs, hadk_bits, kfac);
+    if (st != QTIP_OK) return st;
     if (out == in && out_dtype != in_dtype) return QTIP_ERR_BAD_ARG;
     if (out == in && kfac > 1) return QTIP_ERR_BAD_ARG;  // several CTAs read the whole row
     if (rows == 0) return QTIP_OK;
-    if (rows > 65535) return QTIP_ERR_BAD_SHAPE;
-    int p = 0;
-    while ((1 << p) < len) p++;
-    const size_t smem = (size_t)n * sizeof(float) + (kfac > 1 ? (size_t)kRowsPerCta * kfac * sizeof(float) : 0);
-    if (smem > 227 * 1024) return QTIP_ERR_BAD_SHAPE;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    QTIP_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(rht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr_set[dev] = true;
-    }
-    const int sign_rep = (sign_in || sign_out) ? (int)(n_signs / n) : 1;
-    dim3 grid(kfac > 1 ? (kfac + kRowsPerCta - 1) / kRowsPerCta : 1, (unsigned)rows);
-    rht_kernel<<<grid, kRhtThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        out, out_dtype, in, in_dtype, n, p, sign_in, sign_in_dtype, sign_out, sign_rep, hadk_bits, kfac, transpose,
-        scale);
-    return check_launch();
+    RhtArgs a = {};
+    a.out = out; a.in = in; a.sign_in = sign_in; a.sign_out = sign_out; a.hadk_bits = hadk_bits;
+    a.in_row_stride = n; a.out_dtype = out_dtype; a.in_dtype = in_dtype; a.sign_in_dtype = sign_in_dtype;
+    a.n = n; a.sign_rep = (sign_in || sign_out) ? (int)(n_signs / n) : 1; a.kfac = kfac; a.transpose = transpose;
+    a.scale = scale;
+    return launch_rht(a, rows, stream);
+}
+
+extern "C" int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long rows, long in_row_stride,
+                              int n, const void *residual, void *residual_out, const void *norm_weight, float eps,
+                              const void *gate, const void *sign_in, int sign_in_dtype, const float *sign_out,
+                              long n_signs, const uint32_t *hadk_bits, int kfac, int transpose, float scale,
+                              void *stream) {
+    int st = check_rht(out, out_dtype, in, in_dtype, rows, n, sign_in, sign_in_dtype, sign_out, n_signs, hadk_bits, kfac);
+    if (st != QTIP_OK) return st;
+    if (in_row_stride != 0 && in_row_stride < n) return QTIP_ERR_BAD_ARG;
+    if (residual_out && !residual) return QTIP_ERR_BAD_ARG;
+    // several CTAs (rows with stride 0, or kfac > 1) read the inputs while one writes residual_out / out
+    if (out == in || out == residual || out == gate) return QTIP_ERR_BAD_ARG;
+    if (residual_out && (residual_out == in || residual_out == residual || residual_out == out || residual_out == gate))
+        return QTIP_ERR_BAD_ARG;
+    if (rows == 0) return QTIP_OK;
+    RhtArgs a = {};
+    a.out = out; a.in = in; a.sign_in = sign_in; a.sign_out = sign_out; a.hadk_bits = hadk_bits;
+    a.residual = static_cast<const __half *>(residual); a.residual_out = static_cast<__half *>(residual_out);
+    a.norm_weight = static_cast<const __half *>(norm_weight); a.gate = static_cast<const __half *>(gate);
+    a.in_row_stride = in_row_stride; a.out_dtype = out_dtype; a.in_dtype = in_dtype; a.sign_in_dtype = sign_in_dtype;
+    a.n = n; a.sign_rep = (sign_in || sign_out) ? (int)(n_signs / n) : 1; a.kfac = kfac; a.transpose = transpose;
+    a.scale = scale; a.eps = eps;
+    return launch_rht(a, rows, stream);
 }

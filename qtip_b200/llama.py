@@ -1,0 +1,233 @@
+"""Batch-1 decode loop of a Llama-architecture model whose linears are all QTIP layers.
+
+This is the measurement harness for end-to-end decode speed: a random-init model of a given shape
+(`LlamaShape`), a static KV cache, and one CUDA graph per decode step, replayed once per token
+(upstream: eval/interactive_gen.py:42-85 with model/llama.py; the graph capture follows the pattern
+of lib/utils/graph_wrapper.py:16-47 instead of torch.compile).  Inside the graph a decoder layer is
+17 launches of this library's kernels:
+    RHT-in for q,k,v (one launch, fused residual add + RMSNorm)   3 fused decode-matvecs   RHT-out (one launch)
+    RoPE + KV append     single-query attention
+    RHT-in(o)  matvec  RHT-out
+    RHT-in for gate,up (one launch, fused residual add + RMSNorm)  2 matvecs  RHT-out (one launch)
+    RHT-in(down) with the SwiGLU product fused   matvec   RHT-out
+The embedding lookup, the final norm, the fp16 lm_head and the sampler are plain torch ops.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class LlamaShape:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    head_dim: int = 128
+    mlp: int = 11008
+    vocab: int = 32000
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    K: int = 2  # bits per weight of every linear
+
+
+LLAMA2_7B = LlamaShape()
+
+
+class _Linear:
+    """Buffers of one QTIP linear (the state of QuantizedLinear upstream, lib/linear/quantized_linear.py:41-67)."""
+
+    def __init__(self, m, n, K, gen, device):
+        self.m, self.n, self.K = m, n, K
+        self.codes = torch.randint(0, 65536, (m * n // 256, 16 * K), generator=gen, device=device,
+                                   dtype=torch.int32).to(torch.int16)
+        self.tlut = torch.randn(512, 2, generator=gen, device=device).half()
+        self.SU = (torch.randn(n, generator=gen, device=device).sign() + 1e-5).sign().half()
+        # SV carries the weight scale; keep the layer's output variance about that of its input
+        sv = (torch.randn(m, generator=gen, device=device).sign() + 1e-5).sign().float()
+        self.SV = sv / math.sqrt(n)
+        self.SV32 = (self.SV * 32).contiguous()
+
+
+class QtipLlama:
+
+    def __init__(self, shape=LLAMA2_7B, max_positions=512, device="cuda:0", seed=3000, tp_rank=0, tp_size=1):
+        if tp_size != 1:
+            raise NotImplementedError("tensor-parallel decode lives in qtip_b200.tp")
+        self.shape, self.device, self.max_positions = shape, torch.device(device), max_positions
+        s, dev = shape, self.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        H, KV = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        assert H == s.hidden
+        for d in (s.hidden, KV, s.mlp):
+            assert d % 32 == 0, f"width {d} is not a multiple of 32"
+        assert s.head_dim == 128, "the decode attention kernel is built for head_dim 128"
+        self.layers = []
+        for _ in range(s.n_layers):
+            L = dict(q=_Linear(H, s.hidden, s.K, g, dev), k=_Linear(KV, s.hidden, s.K, g, dev),
+                     v=_Linear(KV, s.hidden, s.K, g, dev), o=_Linear(s.hidden, H, s.K, g, dev),
+                     gate=_Linear(s.mlp, s.hidden, s.K, g, dev), up=_Linear(s.mlp, s.hidden, s.K, g, dev),
+                     down=_Linear(s.hidden, s.mlp, s.K, g, dev))
+            L["ln1"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
+            L["ln2"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
+            # sign vectors of launches that share one input, concatenated
+            L["SU_qkv"] = torch.cat([L["q"].SU, L["k"].SU, L["v"].SU]).contiguous()
+            L["SU_gu"] = torch.cat([L["gate"].SU, L["up"].SU]).contiguous()
+            L["SV_gu"] = torch.cat([L["gate"].SV32, L["up"].SV32]).contiguous()
+            self.layers.append(L)
+        self.embed = (0.02 * torch.randn(s.vocab, s.hidden, generator=g, device=dev)).half()
+        self.lm_head = (0.02 * torch.randn(s.vocab, s.hidden, generator=g, device=dev)).half()
+        self.ln_f = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
+        self.cache_k = torch.zeros(s.n_layers, max_positions, KV, dtype=torch.float16, device=dev)
+        self.cache_v = torch.zeros_like(self.cache_k)
+        # Hadamard factors
+        self.kf_h = ops.had_factor(s.hidden)
+        self.kf_m = ops.had_factor(s.mlp)
+        self.kf_kv = ops.had_factor(KV)
+        self.bits = {}
+        for k in {self.kf_h, self.kf_m, self.kf_kv}:
+            self.bits[k] = None if k == 1 else ops.pack_hadk(ops.get_hadK(k * 2)[0].to(dev))
+        # activations (static, so the step can be captured)
+        f16 = dict(dtype=torch.float16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.token = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.res = [torch.zeros(s.hidden, **f16), torch.zeros(s.hidden, **f16)]  # residual stream, ping-pong
+        self.delta = torch.zeros(s.hidden, **f16)   # output of the last linear, not yet added to the stream
+        self.xh_qkv = torch.zeros(3, s.hidden, **f16)   # RHT-in outputs (fp16 activations of the matvecs)
+        self.xh_gu = torch.zeros(2, s.hidden, **f16)
+        self.xh_o = torch.zeros(H, **f16)
+        self.xh_d = torch.zeros(s.mlp, **f16)
+        self.y_qkv = torch.zeros(H + 2 * KV, **f32)
+        self.qkv = torch.zeros(H + 2 * KV, **f16)
+        self.attn = torch.zeros(H, **f16)
+        self.y_h = torch.zeros(s.hidden, **f32)
+        self.y_gu = torch.zeros(2 * s.mlp, **f32)
+        self.gu = torch.zeros(2 * s.mlp, **f16)
+        self.logits = torch.zeros(1, s.vocab, **f32)
+        self.next_token = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.out_tokens = torch.zeros(max_positions + 1, dtype=torch.int64, device=dev)
+        need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
+                   for (m, n) in ((H, s.hidden), (s.mlp, s.hidden), (s.hidden, s.mlp), (KV, s.hidden)))
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        self.graph = None
+        self.n_launches_per_step = 17 * s.n_layers
+
+    # -- one linear: the three launches ------------------------------------------------------------
+    def _matvec(self, lin, xh, y):
+        ops.decompress_matvec(lin.codes, xh, lin.tlut, lin.K, lin.m, lin.n, out=y.view(1, lin.m), workspace=self.workspace)
+
+    def step(self):
+        """One decode step on the static buffers: token -> next_token, pos += 1.  Capturable."""
+        s = self.shape
+        H, KV = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        res_a, res_b = self.res
+        res_a.copy_(torch.index_select(self.embed, 0, self.token).view(-1))
+        self.delta.zero_()
+        inv_h, inv_m, inv_kv = 1 / math.sqrt(s.hidden), 1 / math.sqrt(s.mlp), 1 / math.sqrt(KV)
+        for li, L in enumerate(self.layers):
+            # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v
+            xh = self.xh_qkv
+            ops.rht_fused(self.delta, 3, s.hidden, xh, in_row_stride=0, residual=res_a, residual_out=res_b,
+                          norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=self.bits[self.kf_h],
+                          kfac=self.kf_h, transpose=True, scale=inv_h / 32)
+            self._matvec(L["q"], xh[0], self.y_qkv[:H])
+            self._matvec(L["k"], xh[1], self.y_qkv[H:H + KV])
+            self._matvec(L["v"], xh[2], self.y_qkv[H + KV:])
+            if H == KV and self.kf_h == self.kf_kv:
+                sv = L.get("SV_qkv")
+                if sv is None:
+                    sv = L["SV_qkv"] = torch.cat([L["q"].SV32, L["k"].SV32, L["v"].SV32]).contiguous()
+                ops.rht_fused(self.y_qkv, 3, H, self.qkv, sign_out=sv, hadk_bits=self.bits[self.kf_h], kfac=self.kf_h,
+                              scale=inv_h)
+            else:
+                ops.rht_fused(self.y_qkv[:H], 1, H, self.qkv[:H], sign_out=L["q"].SV32, hadk_bits=self.bits[self.kf_h],
+                              kfac=self.kf_h, scale=inv_h)
+                sv = L.get("SV_kv")
+                if sv is None:
+                    sv = L["SV_kv"] = torch.cat([L["k"].SV32, L["v"].SV32]).contiguous()
+                ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=self.bits[self.kf_kv],
+                              kfac=self.kf_kv, scale=inv_kv)
+            q, k, v = self.qkv[:H], self.qkv[H:H + KV], self.qkv[H + KV:]
+            ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, s.n_heads, s.n_kv_heads, s.head_dim,
+                               s.rope_theta)
+            ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, s.n_heads, s.n_kv_heads, s.head_dim)
+            # ---- o_proj
+            xo = self.xh_o
+            ops.rht_fused(self.attn, 1, H, xo, sign_in=L["o"].SU, hadk_bits=self.bits[self.kf_h], kfac=self.kf_h,
+                          transpose=True, scale=inv_h / 32)
+            self._matvec(L["o"], xo, self.y_h)
+            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=self.bits[self.kf_h],
+                          kfac=self.kf_h, scale=inv_h)
+            # ---- MLP block: res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up
+            xg = self.xh_gu
+            ops.rht_fused(self.delta, 2, s.hidden, xg, in_row_stride=0, residual=res_b, residual_out=res_a,
+                          norm_weight=L["ln2"], eps=s.rms_eps, sign_in=L["SU_gu"], hadk_bits=self.bits[self.kf_h],
+                          kfac=self.kf_h, transpose=True, scale=inv_h / 32)
+            self._matvec(L["gate"], xg[0], self.y_gu[:s.mlp])
+            self._matvec(L["up"], xg[1], self.y_gu[s.mlp:])
+            ops.rht_fused(self.y_gu, 2, s.mlp, self.gu, sign_out=L["SV_gu"], hadk_bits=self.bits[self.kf_m],
+                          kfac=self.kf_m, scale=inv_m)
+            # ---- down_proj, input silu(gate) * up
+            xd = self.xh_d
+            ops.rht_fused(self.gu[s.mlp:], 1, s.mlp, xd, gate=self.gu[:s.mlp], sign_in=L["down"].SU,
+                          hadk_bits=self.bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
+            self._matvec(L["down"], xd, self.y_h)
+            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=self.bits[self.kf_h],
+                          kfac=self.kf_h, scale=inv_h)
+        # ---- final norm, lm_head, sampler (torch)
+        h = (res_a + self.delta).float()
+        h = (h * torch.rsqrt(h.pow(2).mean() + s.rms_eps)).half() * self.ln_f
+        self.logits.copy_(torch.matmul(h.view(1, -1), self.lm_head.T))
+        self._sample()
+        self.out_tokens.index_copy_(0, self.pos.to(torch.int64) + 1, self.next_token)
+        self.token.copy_(self.next_token)
+        self.pos.add_(1)
+
+    def _sample(self, temperature=0.6, top_k=5):
+        """temperature / top-k sampling without a host sync (eval/interactive_gen.py:15-40 upstream)."""
+        logits = self.logits / max(temperature, 1e-5)
+        v, _ = torch.topk(logits, top_k)
+        logits = torch.where(logits < v[:, -1:], torch.full_like(logits, -float("inf")), logits)
+        probs = torch.softmax(logits, dim=-1)
+        q = torch.empty_like(probs).exponential_(1)
+        self.next_token.copy_(torch.argmax(probs / q, dim=-1))
+
+    # -- driving ----------------------------------------------------------------------------------
+    def capture(self):
+        """Capture step() into a CUDA graph (two eager warm-up steps first; state is restored)."""
+        tok, pos = self.token.clone(), self.pos.clone()
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.step()
+            self.token.copy_(tok); self.pos.copy_(pos)
+            self.step()
+            self.token.copy_(tok); self.pos.copy_(pos)
+            stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                self.step()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.token.copy_(tok); self.pos.copy_(pos)
+        torch.cuda.synchronize(self.device)
+
+    def reset(self):
+        self.pos.zero_()
+        self.cache_k.zero_(); self.cache_v.zero_()
+
+    def feed(self, token_ids):
+        """Run the given tokens through the model one position at a time (fills the KV cache); the
+        sampled continuation of the last one is left in self.token."""
+        run = self.graph.replay if self.graph is not None else self.step
+        for t in token_ids.tolist():
+            self.token.fill_(int(t))
+            run()
+
+    def generate(self, n_tokens):
+        run = self.graph.replay if self.graph is not None else self.step
+        for _ in range(n_tokens):
+            run()

@@ -222,3 +222,34 @@ def hadamard(x, hadK=None, K=1, transpose=False):
     n = x.shape[-1]
     bits = hadk_bits_for(hadK, x.device) if K > 1 else None
     return rht(x, hadk_bits=bits, kfac=K, transpose=transpose, scale=1.0 / math.sqrt(n))
+
+
+def rht_fused(x, rows, n, out, *, in_row_stride=None, residual=None, residual_out=None, norm_weight=None, eps=1e-5,
+              gate=None, sign_in=None, sign_out=None, hadk_bits=None, kfac=1, transpose=False, scale=1.0):
+    """qtip_rht_fused on preallocated tensors (no allocation, graph-capturable); see include/qtip_b200.h."""
+    n_signs = n
+    if sign_in is not None:
+        n_signs = sign_in.numel()
+    if sign_out is not None:
+        n_signs = sign_out.numel()
+    p = lambda t: None if t is None else t.data_ptr()  # noqa: E731
+    st = _lib.load().qtip_rht_fused(out.data_ptr(), _dtype_id(out), x.data_ptr(), _dtype_id(x), rows,
+                                    n if in_row_stride is None else in_row_stride, n, p(residual), p(residual_out),
+                                    p(norm_weight), float(eps), p(gate), p(sign_in),
+                                    F16 if sign_in is None else _dtype_id(sign_in), p(sign_out), n_signs, p(hadk_bits),
+                                    kfac, int(bool(transpose)), float(scale), _stream())
+    _lib.check(st, "qtip_rht_fused")
+    return out
+
+
+def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, theta=10000.0):
+    st = _lib.load().qtip_rope_kv_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+                                         pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), _stream())
+    _lib.check(st, "qtip_rope_kv_append")
+
+
+def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
+    st = _lib.load().qtip_attn_decode(out.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(),
+                                      n_heads, n_kv_heads, head_dim, _stream())
+    _lib.check(st, "qtip_attn_decode")
+    return out

@@ -22,6 +22,15 @@ def test_header_and_binding_agree():
     assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
 
 
+def test_binding_argument_counts_match_header():
+    text = open(os.path.join(ROOT, "include", "qtip_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    for name, params in re.findall(r"\b(qtip_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
+        params = params.strip()
+        count = 0 if params in ("", "void") else params.count(",") + 1
+        assert count == len(_lib.SIGNATURES[name][1]), f"{name}: header has {count} parameters"
+
+
 def test_every_declared_symbol_is_exported():
     lib = ctypes.CDLL(_lib.SO_PATH)
     for name in declared_functions():

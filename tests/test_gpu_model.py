@@ -1,0 +1,112 @@
+"""GPU: the decode harness (17 launches per layer, CUDA graph) against a plain torch evaluation of the same
+random-init model from dense decoded weights - the self-consistency check of the fused path."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import qtip_oracle as O
+from conftest import rel_l2
+from qtip_b200 import ops
+from qtip_b200.llama import LlamaShape, QtipLlama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TINY = LlamaShape(n_layers=2, hidden=256, n_heads=2, n_kv_heads=2, head_dim=128, mlp=1376, vocab=512, K=2)
+
+
+def had_matrix(n):
+    """Dense orthonormal Hadamard matrix of the transform x -> hadamard(x) (float64, from the oracle)."""
+    k = O.had_factor(n)
+    hk = None if k == 1 else ops.get_hadK(n)[0].numpy()
+    return torch.from_numpy(O.hadamard(np.eye(n), hk)).T.contiguous()  # row i of eye -> column i
+
+
+def dense_linear(lin, x, Hn, Hm):
+    """y = Had_m( (Had_n^T (x*SU) / 32).half @ W^T ) * SV*32 in float64 (BitshiftLinear.forward upstream)."""
+    W = ops.decode_hyb(lin.codes, lin.tlut, lin.K, lin.m, lin.n).double()
+    xs = (x.double() * lin.SU.double()) @ Hn.to(x.device) / 32       # Hn is H^T applied from the right: x @ H^T... see below
+    y = xs.half().double() @ W.T
+    return (y @ Hm.to(x.device)) * lin.SV32.double()
+
+
+def reference_logits(model, tokens):
+    s = model.shape
+    H = s.n_heads * s.head_dim
+    # hadamard(x) = Hmat @ x  =>  for row vectors x @ Hmat.T ; the input side uses the transposed transform
+    Hh, Hm_ = had_matrix(s.hidden).to(DEV), had_matrix(s.mlp).to(DEV)
+    # forward transform of a row vector: x @ Hmat.T ; transposed transform: x @ Hmat
+    fwd = {s.hidden: Hh.T.contiguous(), s.mlp: Hm_.T.contiguous()}
+    tr = {s.hidden: Hh, s.mlp: Hm_}
+    ks, vs = [[] for _ in range(s.n_layers)], [[] for _ in range(s.n_layers)]
+    logits = None
+    for pos, tok in enumerate(tokens):
+        x = model.embed[tok].double()
+
+        def norm(v, w):
+            v32 = v.float()
+            hn = (v32 * torch.rsqrt(v32.pow(2).mean() + s.rms_eps)).half()
+            return (w * hn).double()
+
+        def lin(l, v):
+            return dense_linear(l, v, tr[l.n], fwd[l.m]).half().double()
+
+        for li, L in enumerate(model.layers):
+            h = norm(x.half(), L["ln1"])
+            q, k, v = lin(L["q"], h), lin(L["k"], h), lin(L["v"], h)
+            half = s.head_dim // 2
+            inv = s.rope_theta ** (-torch.arange(half, device=DEV, dtype=torch.float64) * 2 / s.head_dim)
+            cs, sn = torch.cos(pos * inv), torch.sin(pos * inv)
+
+            def rope(t):
+                t = t.view(-1, s.head_dim)
+                a, b = t[:, :half], t[:, half:]
+                return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=1).half().double()
+
+            q, k = rope(q), rope(k)
+            ks[li].append(k); vs[li].append(v.view(-1, s.head_dim))
+            Kc, Vc = torch.stack(ks[li], 1), torch.stack(vs[li], 1)            # (heads, ctx, hd)
+            att = torch.softmax((q.unsqueeze(1) @ Kc.transpose(1, 2)) / math.sqrt(s.head_dim), dim=-1) @ Vc
+            x = (x.half() + lin(L["o"], att.reshape(-1).half().double()).half()).double()
+            h = norm(x.half(), L["ln2"])
+            g, u = lin(L["gate"], h), lin(L["up"], h)
+            act = (torch.nn.functional.silu(g.float()).half() * u.half()).double()
+            x = (x.half() + lin(L["down"], act).half()).double()
+        h = norm(x.half(), model.ln_f)
+        logits = h.half().float() @ model.lm_head.float().T
+    return logits
+
+
+def test_decode_step_matches_dense_reference():
+    torch.manual_seed(0)
+    model = QtipLlama(TINY, max_positions=16, device=DEV, seed=11)
+    tokens = [3, 77, 400, 9, 250]
+    model.reset()
+    for t in tokens:
+        model.token.fill_(t)
+        model.step()
+    got = model.logits.clone()
+    want = reference_logits(model, tokens)
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 2e-2
+    assert int(model.pos.item()) == len(tokens)
+
+
+def test_graph_replay_matches_eager():
+    model = QtipLlama(TINY, max_positions=16, device=DEV, seed=12)
+    tokens = torch.tensor([5, 6, 7, 8])
+    model.reset()
+    for t in tokens.tolist():
+        model.token.fill_(t)
+        model.step()
+    eager = model.logits.clone()
+    model.reset()
+    model.capture()
+    model.reset()
+    model.feed(tokens)
+    torch.cuda.synchronize()
+    assert torch.equal(model.logits, eager)
+    model.generate(3)
+    torch.cuda.synchronize()
+    assert int(model.pos.item()) == 7
+    assert torch.all(model.out_tokens[1:8] >= 0) and torch.all(model.out_tokens[1:8] < TINY.vocab)
