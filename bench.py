@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark: batch-1 decode tokens/s of a random-init Llama-2-7B-shaped model whose linears are all
+2-bit HYB QTIP layers (128-token prompt, then timed decode steps from one CUDA graph), plus the
+roofline of the dominant kernel (the fused decode-matvec) and a CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl qtip_b200|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one decoded token.  Under torchrun (N > 1) each rank
+drives one GPU.  `--impl reference` times the CPU port of the upstream path (oracle/) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bs=1 decode tok/s (Llama-2-7B-shape, 2-bit HYB)"
+PROMPT_TOKENS = 128
+PUBLISHED_TOK_S = 188.0  # upstream README.md:31-38, Llama-2-7B 2-bit on an RTX 6000 Ada (fused q/k/v and up/gate)
+# DRAM bytes (read + write) of one decode-matvec launch from an ncu capture (profiles/matvec_hyb_llama7b_k2.md)
+NCU_TRAFFIC_BYTES = {(4096, 4096): None, (11008, 4096): None, (4096, 11008): None}
+
+
+def llama7b_linears():
+    """(m, n) of the seven linears of a decoder layer: q, k, v, o, gate, up, down."""
+    return [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+
+
+def algorithmic_bytes(m, n, K, bs=1):
+    """Packed codes read once plus fp16 activations in and out (per layer call)."""
+    return m * n * K // 8 + 2 * bs * (m + n)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU port of the upstream path (oracle/): used as the reported baseline and as the reference arm
+# ---------------------------------------------------------------------------------------------------------
+def cpu_layer_seconds(repeats=3, K=2):
+    """Wall time of the seven QTIP linears of one Llama-2-7B decoder layer (1/32 of a token's linear work)
+    through the C restatement, all host threads.  Returns (seconds, threads)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import c_oracle as C
+    from qtip_b200 import ops, synth
+    times = []
+    lays = {}
+    for (m, n) in set(llama7b_linears()):
+        lay = synth.make_layer(m, n, K, seed=1000 + m // 64 + n)
+        hl, hr = ops.get_hadK(n)[0], ops.get_hadK(m)[0]
+        lays[(m, n)] = (lay, None if hl is None else hl.numpy(), None if hr is None else hr.numpy())
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for (m, n) in llama7b_linears():
+            lay, hl, hr = lays[(m, n)]
+            C.layer_forward(lay["x"].astype(np.float32), lay["codes"], m, n, K, lay["tlut"],
+                            lay["SU"].astype(np.float32), lay["SV"], hl, hr)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), C.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    for i in range(args.warmup + args.steps):
+        sec, threads = cpu_layer_seconds(repeats=1)
+        if i >= args.warmup:
+            per_step.append(sec * 32)  # 32 decoder layers per token
+    ms = statistics.mean(per_step) * 1e3
+    value = 1e3 / ms
+    sample = ("each step = the seven QTIP linears of one decoder layer (Hadamard in, decode + matvec, Hadamard out) "
+              "timed once and scaled by 32 layers; attention, norms and lm_head are not included")
+    out = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f16", "data": "synthetic",
+           "config": {"workload": "Llama-2-7B shape, all linears 2-bit HYB QTIP, batch 1, 128-token prompt, decode"},
+           "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+           "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------
+def measure_matvec_roofline(model, torch, reps=5):
+    """Average duration of one fused decode-matvec launch: all 7 x n_layers launches of a token, every one on
+    its own weights (1.6 GB in total, far beyond L2), captured in one graph and timed with CUDA events."""
+    from qtip_b200 import ops
+    s = model.shape
+    dev = model.device
+    xh = {n: torch.randn(n, device=dev).half() for n in (s.hidden, s.mlp)}
+    ys = {m: torch.zeros(m, dtype=torch.float32, device=dev) for m in (s.hidden, s.mlp)}
+
+    def all_matvecs():
+        for L in model.layers:
+            for name in ("q", "k", "v", "o", "gate", "up", "down"):
+                lin = L[name]
+                ops.decompress_matvec(lin.codes, xh[lin.n], lin.tlut, lin.K, lin.m, lin.n, out=ys[lin.m].view(1, -1),
+                                      workspace=model.workspace)
+
+    stream = torch.cuda.Stream(device=dev)
+    stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(stream):
+        all_matvecs()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            all_matvecs()
+    torch.cuda.current_stream(dev).wait_stream(stream)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    launches = 7 * s.n_layers
+    us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
+    byts = sum(algorithmic_bytes(m, n, s.K) for (m, n) in llama7b_linears()) / 7
+    return us, byts, launches
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from qtip_b200.llama import LLAMA2_7B, QtipLlama
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    model = QtipLlama(LLAMA2_7B, max_positions=args.prompt + 2 * (warmup + steps) + 8, device=dev, seed=3000 + rank)
+    model.capture()
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, LLAMA2_7B.vocab, (args.prompt,), generator=g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def prefill():
+        model.reset()
+        model.feed(prompt)
+        model.generate(warmup)
+
+    # ---- device-timed decode: K graph replays, tokens stay on the device --------------------------------
+    prefill()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        model.generate(steps)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+
+    # ---- end to end: every step the token goes host -> device (pinned) and the sampled token comes back ----
+    prefill()
+    h_tok = torch.zeros(1, dtype=torch.int64).pin_memory()
+    h_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    h_tok.copy_(model.token.cpu())
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        model.token.copy_(h_tok, non_blocking=True)
+        model.graph.replay()
+        h_out.copy_(model.next_token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        h_tok[0] = h_out[0]
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+
+    out = None
+    if rank == 0:
+        us, byts, launches = measure_matvec_roofline(model, torch)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        achieved = byts / us / 1e3  # GB/s
+        traffic = [NCU_TRAFFIC_BYTES.get(s) for s in llama7b_linears()]
+        traffic = None if any(t is None for t in traffic) else sum(traffic) / len(traffic)
+        sec, threads = cpu_layer_seconds(repeats=3)
+        cpu_tok_s = 1.0 / (32 * sec)
+        out = {
+            "metric": METRIC, "value": world * steps / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": world * steps / (ms / 1e3) / PUBLISHED_TOK_S, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "Llama-2-7B shape (32 layers, hidden 4096, 32 heads, MLP 11008, vocab 32000), every linear "
+                                   "2-bit HYB QTIP (L=16, Q=9, V=2, 16x16 tiles), batch 1, 128-token prompt, CUDA-graph decode",
+                       "l2": "each step streams 1.6 GB of packed codes and a 262 MB lm_head, far larger than L2",
+                       "replicas": world},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "kernel": "matvec_hyb_kernel<2>", "us_per_launch": us,
+                         "algorithmic_bytes_per_launch": byts, "peak_source": "MEASURED_PEAKS.json hbm_gbs"
+                         if "hbm_gbs" in peaks else "fallback 6650 GB/s"},
+            "cpu_baseline": {"value": cpu_tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": "the seven QTIP linears of one decoder layer through the C restatement "
+                                       "(median of 3), scaled by 32 layers; attention, norms, lm_head not included"},
+            "e2e": {"value": world * steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 8,
+                    "d2h_bytes_per_step": 8},
+            "gpu_launches": model.n_launches_per_step * steps,
+            "clocks": clocks.summary(),
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=PROMPT_TOKENS, help="prompt length (128 in the benchmark configuration)")
+    ap.add_argument("--impl", default="qtip_b200", choices=["qtip_b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
