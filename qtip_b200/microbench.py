@@ -1,0 +1,107 @@
+"""Per-layer sweep of the fused decode-matvec (and the other kernels) on synthetic weights.
+
+    python -m qtip_b200.microbench                       # Llama-2-7B shapes, K = 2, 3, 4, batch 1
+    python -m qtip_b200.microbench --shapes 8192x8192,28672x8192 --bits 2 --batch 1,4,8
+    python -m qtip_b200.microbench --shapes 4096x11008 --bits 2 --plain-launches 8   # for a profiler
+
+Timing method (the one of qtip-kernels/test_decompress_matvec.py:69-91 upstream, scaled up): the
+launches of one measurement walk over enough distinct weight sets to exceed the 126 MB L2, are
+captured in one CUDA graph, and the graph is replayed between two CUDA events.  GB/s counts the
+algorithmic bytes m*n*K/8 + 2*bs*(m+n).  Shapes are written out_features x in_features.
+"""
+import argparse
+import json
+
+import torch
+
+from . import _lib, ops, synth
+
+LLAMA7B = "4096x4096,11008x4096,4096x11008"
+
+
+def _sets(m, n, K, bs, code, device, min_bytes=400e6, max_sets=48):
+    per = m * n * K // 8
+    nset = int(min(max_sets, max(3, min_bytes // per)))
+    return [synth.make_layer(m, n, K, seed=i, bs=bs, code=code, device=device) for i in range(nset)]
+
+
+def _launch(lay, code, K, m, n, out, ws):
+    if code == "hyb":
+        ops.decompress_matvec(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out, workspace=ws)
+    else:
+        ops.decompress_matvec_plain(lay["codes"], lay["x"], code, K, m, n, out=out, workspace=ws)
+
+
+def time_matvec(m, n, K, bs=1, code="hyb", device="cuda:0", replays=20):
+    lays = _sets(m, n, K, bs, code, device)
+    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, bs), dtype=torch.uint8, device=device)
+    out = torch.empty(bs, m, device=device)
+    stream = torch.cuda.Stream(device=device)
+    stream.wait_stream(torch.cuda.current_stream(device))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        _launch(lays[0], code, K, m, n, out, ws)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for lay in lays:
+                _launch(lay, code, K, m, n, out, ws)
+    torch.cuda.current_stream(device).wait_stream(stream)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / (replays * len(lays))
+    byts = m * n * K / 8 + 2 * bs * (m + n)
+    return dict(code=code, K=K, m=m, n=n, bs=bs, us=us, gbs=byts / us / 1e3, weight_sets=len(lays))
+
+
+def plain_launches(m, n, K, bs, code, count, device="cuda:0"):
+    """`count` ordinary stream launches over rotating weight sets (what a profiler should capture)."""
+    lays = _sets(m, n, K, bs, code, device, min_bytes=160e6, max_sets=14)
+    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, bs), dtype=torch.uint8, device=device)
+    out = torch.empty(bs, m, device=device)
+    for i in range(count):
+        _launch(lays[i % len(lays)], code, K, m, n, out, ws)
+    torch.cuda.synchronize(device)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default=LLAMA7B)
+    ap.add_argument("--bits", default="2,3,4")
+    ap.add_argument("--batch", default="1")
+    ap.add_argument("--code", default="hyb", choices=["hyb", "3inst", "1mad"])
+    ap.add_argument("--plain-launches", type=int, default=0)
+    ap.add_argument("--json", action="store_true")
+    args = ap.parse_args()
+    peak = None
+    try:
+        import os
+        peak = json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                           "MEASURED_PEAKS.json")))["hbm_gbs"]
+    except (OSError, KeyError):
+        pass
+    rows = []
+    for K in (int(b) for b in args.bits.split(",")):
+        for shape in args.shapes.split(","):
+            m, n = (int(v) for v in shape.split("x"))
+            for bs in (int(b) for b in args.batch.split(",")):
+                if args.plain_launches:
+                    plain_launches(m, n, K, bs, args.code, args.plain_launches)
+                    continue
+                r = time_matvec(m, n, K, bs, args.code)
+                rows.append(r)
+                frac = f"  {100 * r['gbs'] / peak:5.1f}% of measured HBM peak" if peak else ""
+                if not args.json:
+                    print(f"{args.code} K={K} {m}x{n} bs={bs}: {r['us']:8.2f} us  {r['gbs']:7.0f} GB/s{frac}", flush=True)
+    if args.json:
+        print(json.dumps(rows))
+
+
+if __name__ == "__main__":
+    main()
