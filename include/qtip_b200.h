@@ -30,7 +30,8 @@ enum {
     QTIP_ERR_BAD_SHAPE = 2,    /* m or n not a multiple of the tile block, size has no Hadamard factorisation */
     QTIP_ERR_WORKSPACE = 3,    /* workspace missing or too small */
     QTIP_ERR_CUDA = 4,         /* a CUDA runtime call or the launch failed; see qtip_last_cuda_error() */
-    QTIP_ERR_ALIGNMENT = 5     /* a pointer is not aligned as documented */
+    QTIP_ERR_ALIGNMENT = 5,    /* a pointer is not aligned as documented */
+    QTIP_ERR_TOO_LARGE = 6     /* the problem needs more scratch than the built-in array of qtip_decompress_matvec_static */
 };
 
 enum { QTIP_CODE_HYB = 0, QTIP_CODE_3INST = 1, QTIP_CODE_1MAD = 2 };
@@ -77,7 +78,23 @@ size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
 int qtip_decompress_matvec(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
                            int bs, void *workspace, size_t workspace_bytes, void *stream);
 
-/* 3INST / 1MAD, plain layout, V=1; same contract as above (no LUT).  The decoded weights are the
+/* qtip_decompress_matvec for callers that must not allocate device memory and have none to spare for a
+ * workspace - a serving loop that froze its memory pool at start-up, a plug-in whose host owns every
+ * allocation, code running where a cudaMalloc would synchronise the device.  (No counterpart in the
+ * reference, whose kernel needs no scratch.)  Same arguments and result as qtip_decompress_matvec minus
+ * the workspace: the ticket counters and partial sums live in a 4 MiB + 64.25 KiB array built into the
+ * library's device image (each GPU that loads the library holds it until the process exits).  Problems
+ * whose qtip_matvec_workspace_bytes(m, n, bs) exceeds that size return QTIP_ERR_TOO_LARGE; every
+ * Llama-2/3 layer shape up to 53248 x 16384 fits.  The call itself performs no cudaMalloc / cudaFree
+ * and calls no allocating library routine.  The FIRST call on each device looks the array's device
+ * address up (cudaGetSymbolAddress, with that device current) - make that call outside any stream
+ * capture.  All calls on a device share the one array: its ticket counters are cleared on `stream`
+ * before each launch, and two calls that can overlap on the GPU (different streams, or graph branches)
+ * race - serialise them or use qtip_decompress_matvec with separate workspaces. */
+int qtip_decompress_matvec_static(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
+                                  int bs, void *stream);
+
+/* 3INST / 1MAD, plain layout, V=1; same contract as qtip_decompress_matvec (no LUT).  The decoded weights are the
  * ones qtip_decode_plain produces.  m, n multiples of 32. */
 int qtip_decompress_matvec_plain(float *out, const void *codes, const void *x, int code, int K, int m, int n,
                                  int bs, void *workspace, size_t workspace_bytes, void *stream);

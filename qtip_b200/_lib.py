@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 SO_PATH = os.path.join(_HERE, "libqtip_b200.so")
 
-OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_WORKSPACE, ERR_CUDA, ERR_ALIGNMENT = range(6)
+OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_WORKSPACE, ERR_CUDA, ERR_ALIGNMENT, ERR_TOO_LARGE = range(7)
 CODE_HYB, CODE_3INST, CODE_1MAD = 0, 1, 2
 F16, F32 = 0, 1
 
@@ -24,6 +24,7 @@ SIGNATURES = {
     "qtip_decode_plain": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "qtip_matvec_workspace_bytes": (_sz, [_i, _i, _i]),
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "qtip_decompress_matvec_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,

@@ -29,6 +29,7 @@ extern "C" const char *qtip_status_string(int status) {
         case QTIP_ERR_WORKSPACE: return "workspace missing or too small";
         case QTIP_ERR_CUDA: return "CUDA error (see qtip_last_cuda_error)";
         case QTIP_ERR_ALIGNMENT: return "pointer not aligned as required";
+        case QTIP_ERR_TOO_LARGE: return "problem needs more scratch than the built-in array of qtip_decompress_matvec_static (4 MiB)";
         default: return "unknown status";
     }
 }

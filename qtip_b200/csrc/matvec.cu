@@ -36,6 +36,7 @@
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -581,4 +582,53 @@ extern "C" int qtip_decompress_matvec_plain(float *out, const void *codes, const
         matvec_plain_kernel<QTIP_CODE_1MAD><<<p.grid, kPlainWarps * 32, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax,
                                                                                  p.mode, ws);
     return check_launch();
+}
+
+// ---- allocation-free variant ------------------------------------------------------------------------------
+// Scratch (ticket counters + partial sums) of qtip_decompress_matvec_static: a fixed array in the
+// library's device image.  Every GPU that loads the library carries these 4 MiB + 64.25 KiB until the
+// process exits.  In host code the name below is only a stand-in for the symbol; the address a kernel
+// can use comes from cudaGetSymbolAddress, looked up once per device.
+namespace qtip {
+namespace {
+constexpr size_t kStaticScratchBytes = kPartialOffset + 4u * 1024u * 1024u;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+std::mutex g_static_scratch_mutex;
+void *g_static_scratch_ptr[64] = {};
+}  // namespace
+}  // namespace qtip
+
+extern "C" int qtip_decompress_matvec_static(float *out, const void *codes, const void *x, const void *tlut, int K,
+                                             int m, int n, int bs, void *stream) {
+    if (!tlut) return QTIP_ERR_BAD_ARG;
+    if (m > 0 && n > 0 && !(m & 31) && !(n & 31) && qtip_matvec_workspace_bytes(m, n, bs) > kStaticScratchBytes)
+        return QTIP_ERR_TOO_LARGE;
+    int dev = 0;
+    QTIP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return QTIP_ERR_BAD_ARG;
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_ptr[dev]) {
+            // first call on this device (it is the current one): resolve the device address of the array
+            void *p = nullptr;
+            QTIP_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+            g_static_scratch_ptr[dev] = p;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    int st = check_common(out, codes, x, K, m, n, bs, scratch, kStaticScratchBytes);
+    if (st != QTIP_OK) return st;
+    if (!aligned(tlut, 4)) return QTIP_ERR_ALIGNMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call (or an interrupted one) left: the ticket counters of the
+    // row blocks this call uses must start at zero
+    QTIP_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)(m >> 5) * sizeof(unsigned), s));
+    auto *c = static_cast<const uint8_t *>(codes);
+    auto *xh = static_cast<const __half *>(x);
+    auto *t = static_cast<const uint32_t *>(tlut);
+    auto *ws = static_cast<uint8_t *>(scratch);
+    if (K == 2) return launch_hyb<2>(out, c, xh, t, m, n, bs, ws, s);
+    if (K == 3) return launch_hyb<3>(out, c, xh, t, m, n, bs, ws, s);
+    return launch_hyb<4>(out, c, xh, t, m, n, bs, ws, s);
 }
