@@ -38,39 +38,53 @@ LLAMA2_7B = LlamaShape()
 
 
 class _Linear:
-    """Buffers of one QTIP linear (the state of QuantizedLinear upstream, lib/linear/quantized_linear.py:41-67)."""
+    """Buffers of one (shard of a) QTIP linear - the state of QuantizedLinear upstream
+    (lib/linear/quantized_linear.py:41-67).  m, n are the LOCAL sizes; `split` says which side is sharded
+    ("col": rows of the full matrix, "row": columns, None: not sharded).  Codes and LUT come from the local
+    generator, the sign vectors from the shared one (all ranks draw the full vectors and keep their slice)."""
 
-    def __init__(self, m, n, K, gen, device):
+    def __init__(self, m, n, K, g_local, g_shared, device, split=None, rank=0, tp=1):
         self.m, self.n, self.K = m, n, K
-        self.codes = torch.randint(0, 65536, (m * n // 256, 16 * K), generator=gen, device=device,
+        self.codes = torch.randint(0, 65536, (m * n // 256, 16 * K), generator=g_local, device=device,
                                    dtype=torch.int32).to(torch.int16)
-        self.tlut = torch.randn(512, 2, generator=gen, device=device).half()
-        self.SU = (torch.randn(n, generator=gen, device=device).sign() + 1e-5).sign().half()
+        self.tlut = torch.randn(512, 2, generator=g_shared, device=device).half()
+        n_full = n * tp if split == "row" else n
+        m_full = m * tp if split == "col" else m
+        SU = (torch.randn(n_full, generator=g_shared, device=device).sign() + 1e-5).sign().half()
         # SV carries the weight scale; keep the layer's output variance about that of its input
-        sv = (torch.randn(m, generator=gen, device=device).sign() + 1e-5).sign().float()
-        self.SV = sv / math.sqrt(n)
+        SV = (torch.randn(m_full, generator=g_shared, device=device).sign() + 1e-5).sign().float() / math.sqrt(n_full)
+        self.SU = SU[rank * n:(rank + 1) * n].contiguous() if split == "row" else SU
+        self.SV = SV[rank * m:(rank + 1) * m].contiguous() if split == "col" else SV
         self.SV32 = (self.SV * 32).contiguous()
 
 
 class QtipLlama:
 
-    def __init__(self, shape=LLAMA2_7B, max_positions=512, device="cuda:0", seed=3000, tp_rank=0, tp_size=1):
-        if tp_size != 1:
-            raise NotImplementedError("tensor-parallel decode lives in qtip_b200.tp")
+    def __init__(self, shape=LLAMA2_7B, max_positions=512, device="cuda:0", seed=3000, tp_rank=0, tp_size=1,
+                 group=None):
+        """tp_size > 1: this process holds rank tp_rank's shards (qtip_b200.tp) and `group` is the
+        torch.distributed group of the tp_size ranks (one all-reduce after o_proj and after down_proj)."""
         self.shape, self.device, self.max_positions = shape, torch.device(device), max_positions
-        s, dev = shape, self.device
-        g = torch.Generator(device=dev).manual_seed(seed)
-        H, KV = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
-        assert H == s.hidden
-        for d in (s.hidden, KV, s.mlp):
+        self.tp, self.rank, self.group = tp_size, tp_rank, group
+        s, dev, tp = shape, self.device, tp_size
+        g = torch.Generator(device=dev).manual_seed(seed)                              # shared across ranks
+        gl = torch.Generator(device=dev).manual_seed(seed + 7919 * (tp_rank + 1))      # this rank's shards
+        assert s.n_heads % tp == 0 and s.n_kv_heads % tp == 0 and s.mlp % tp == 0
+        H, KV, MLP = s.n_heads * s.head_dim // tp, s.n_kv_heads * s.head_dim // tp, s.mlp // tp   # LOCAL widths
+        self.H, self.KV, self.MLP = H, KV, MLP
+        self.n_heads, self.n_kv_heads = s.n_heads // tp, s.n_kv_heads // tp
+        assert s.n_heads * s.head_dim == s.hidden
+        for d in (s.hidden, H, KV, MLP):
             assert d % 32 == 0, f"width {d} is not a multiple of 32"
         assert s.head_dim == 128, "the decode attention kernel is built for head_dim 128"
+        col = dict(split="col" if tp > 1 else None, rank=tp_rank, tp=tp)
+        row = dict(split="row" if tp > 1 else None, rank=tp_rank, tp=tp)
         self.layers = []
         for _ in range(s.n_layers):
-            L = dict(q=_Linear(H, s.hidden, s.K, g, dev), k=_Linear(KV, s.hidden, s.K, g, dev),
-                     v=_Linear(KV, s.hidden, s.K, g, dev), o=_Linear(s.hidden, H, s.K, g, dev),
-                     gate=_Linear(s.mlp, s.hidden, s.K, g, dev), up=_Linear(s.mlp, s.hidden, s.K, g, dev),
-                     down=_Linear(s.hidden, s.mlp, s.K, g, dev))
+            L = dict(q=_Linear(H, s.hidden, s.K, gl, g, dev, **col), k=_Linear(KV, s.hidden, s.K, gl, g, dev, **col),
+                     v=_Linear(KV, s.hidden, s.K, gl, g, dev, **col), o=_Linear(s.hidden, H, s.K, gl, g, dev, **row),
+                     gate=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col), up=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col),
+                     down=_Linear(s.hidden, MLP, s.K, gl, g, dev, **row))
             L["ln1"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
             L["ln2"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
             # sign vectors of launches that share one input, concatenated
@@ -83,12 +97,13 @@ class QtipLlama:
         self.ln_f = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
         self.cache_k = torch.zeros(s.n_layers, max_positions, KV, dtype=torch.float16, device=dev)
         self.cache_v = torch.zeros_like(self.cache_k)
-        # Hadamard factors
+        # Hadamard factors: full hidden width, and the local chunks of the split sides
         self.kf_h = ops.had_factor(s.hidden)
-        self.kf_m = ops.had_factor(s.mlp)
+        self.kf_hl = ops.had_factor(H)
+        self.kf_m = ops.had_factor(MLP)
         self.kf_kv = ops.had_factor(KV)
         self.bits = {}
-        for k in {self.kf_h, self.kf_m, self.kf_kv}:
+        for k in {self.kf_h, self.kf_hl, self.kf_m, self.kf_kv}:
             self.bits[k] = None if k == 1 else ops.pack_hadk(ops.get_hadK(k * 2)[0].to(dev))
         # activations (static, so the step can be captured)
         f16 = dict(dtype=torch.float16, device=dev)
@@ -100,83 +115,92 @@ class QtipLlama:
         self.xh_qkv = torch.zeros(3, s.hidden, **f16)   # RHT-in outputs (fp16 activations of the matvecs)
         self.xh_gu = torch.zeros(2, s.hidden, **f16)
         self.xh_o = torch.zeros(H, **f16)
-        self.xh_d = torch.zeros(s.mlp, **f16)
+        self.xh_d = torch.zeros(MLP, **f16)
         self.y_qkv = torch.zeros(H + 2 * KV, **f32)
         self.qkv = torch.zeros(H + 2 * KV, **f16)
         self.attn = torch.zeros(H, **f16)
         self.y_h = torch.zeros(s.hidden, **f32)
-        self.y_gu = torch.zeros(2 * s.mlp, **f32)
-        self.gu = torch.zeros(2 * s.mlp, **f16)
+        self.y_gu = torch.zeros(2 * MLP, **f32)
+        self.gu = torch.zeros(2 * MLP, **f16)
         self.logits = torch.zeros(1, s.vocab, **f32)
         self.next_token = torch.zeros(1, dtype=torch.int64, device=dev)
         self.out_tokens = torch.zeros(max_positions + 1, dtype=torch.int64, device=dev)
         need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
-                   for (m, n) in ((H, s.hidden), (s.mlp, s.hidden), (s.hidden, s.mlp), (KV, s.hidden)))
+                   for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
         self.graph = None
-        self.n_launches_per_step = 17 * s.n_layers
+        self.n_launches_per_step = (17 if H == KV and self.kf_hl == self.kf_kv else 18) * s.n_layers
 
     # -- one linear: the three launches ------------------------------------------------------------
     def _matvec(self, lin, xh, y):
         ops.decompress_matvec(lin.codes, xh, lin.tlut, lin.K, lin.m, lin.n, out=y.view(1, lin.m), workspace=self.workspace)
 
+    def _all_reduce(self, t):
+        if self.tp > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+
     def step(self):
         """One decode step on the static buffers: token -> next_token, pos += 1.  Capturable."""
         s = self.shape
-        H, KV = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        H, KV, MLP = self.H, self.KV, self.MLP
         res_a, res_b = self.res
         res_a.copy_(torch.index_select(self.embed, 0, self.token).view(-1))
         self.delta.zero_()
-        inv_h, inv_m, inv_kv = 1 / math.sqrt(s.hidden), 1 / math.sqrt(s.mlp), 1 / math.sqrt(KV)
+        inv_h, inv_hl, inv_m, inv_kv = (1 / math.sqrt(d) for d in (s.hidden, H, MLP, KV))
+        bits = self.bits
         for li, L in enumerate(self.layers):
-            # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v
+            # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v (column-parallel)
             xh = self.xh_qkv
             ops.rht_fused(self.delta, 3, s.hidden, xh, in_row_stride=0, residual=res_a, residual_out=res_b,
-                          norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=self.bits[self.kf_h],
+                          norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=bits[self.kf_h],
                           kfac=self.kf_h, transpose=True, scale=inv_h / 32)
             self._matvec(L["q"], xh[0], self.y_qkv[:H])
             self._matvec(L["k"], xh[1], self.y_qkv[H:H + KV])
             self._matvec(L["v"], xh[2], self.y_qkv[H + KV:])
-            if H == KV and self.kf_h == self.kf_kv:
+            if H == KV and self.kf_hl == self.kf_kv:
                 sv = L.get("SV_qkv")
                 if sv is None:
                     sv = L["SV_qkv"] = torch.cat([L["q"].SV32, L["k"].SV32, L["v"].SV32]).contiguous()
-                ops.rht_fused(self.y_qkv, 3, H, self.qkv, sign_out=sv, hadk_bits=self.bits[self.kf_h], kfac=self.kf_h,
-                              scale=inv_h)
+                ops.rht_fused(self.y_qkv, 3, H, self.qkv, sign_out=sv, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
+                              scale=inv_hl)
             else:
-                ops.rht_fused(self.y_qkv[:H], 1, H, self.qkv[:H], sign_out=L["q"].SV32, hadk_bits=self.bits[self.kf_h],
-                              kfac=self.kf_h, scale=inv_h)
+                ops.rht_fused(self.y_qkv[:H], 1, H, self.qkv[:H], sign_out=L["q"].SV32, hadk_bits=bits[self.kf_hl],
+                              kfac=self.kf_hl, scale=inv_hl)
                 sv = L.get("SV_kv")
                 if sv is None:
                     sv = L["SV_kv"] = torch.cat([L["k"].SV32, L["v"].SV32]).contiguous()
-                ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=self.bits[self.kf_kv],
+                ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=bits[self.kf_kv],
                               kfac=self.kf_kv, scale=inv_kv)
             q, k, v = self.qkv[:H], self.qkv[H:H + KV], self.qkv[H + KV:]
-            ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, s.n_heads, s.n_kv_heads, s.head_dim,
-                               s.rope_theta)
-            ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, s.n_heads, s.n_kv_heads, s.head_dim)
-            # ---- o_proj
+            ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                               s.head_dim, s.rope_theta)
+            ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                            s.head_dim)
+            # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
             xo = self.xh_o
-            ops.rht_fused(self.attn, 1, H, xo, sign_in=L["o"].SU, hadk_bits=self.bits[self.kf_h], kfac=self.kf_h,
-                          transpose=True, scale=inv_h / 32)
+            ops.rht_fused(self.attn, 1, H, xo, sign_in=L["o"].SU, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
+                          transpose=True, scale=inv_hl / 32)
             self._matvec(L["o"], xo, self.y_h)
-            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=self.bits[self.kf_h],
+            self._all_reduce(self.y_h)
+            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=bits[self.kf_h],
                           kfac=self.kf_h, scale=inv_h)
-            # ---- MLP block: res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up
+            # ---- MLP block: res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up (column-parallel)
             xg = self.xh_gu
             ops.rht_fused(self.delta, 2, s.hidden, xg, in_row_stride=0, residual=res_b, residual_out=res_a,
-                          norm_weight=L["ln2"], eps=s.rms_eps, sign_in=L["SU_gu"], hadk_bits=self.bits[self.kf_h],
+                          norm_weight=L["ln2"], eps=s.rms_eps, sign_in=L["SU_gu"], hadk_bits=bits[self.kf_h],
                           kfac=self.kf_h, transpose=True, scale=inv_h / 32)
-            self._matvec(L["gate"], xg[0], self.y_gu[:s.mlp])
-            self._matvec(L["up"], xg[1], self.y_gu[s.mlp:])
-            ops.rht_fused(self.y_gu, 2, s.mlp, self.gu, sign_out=L["SV_gu"], hadk_bits=self.bits[self.kf_m],
+            self._matvec(L["gate"], xg[0], self.y_gu[:MLP])
+            self._matvec(L["up"], xg[1], self.y_gu[MLP:])
+            ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
                           kfac=self.kf_m, scale=inv_m)
-            # ---- down_proj, input silu(gate) * up
+            # ---- down_proj (row-parallel), input silu(gate) * up
             xd = self.xh_d
-            ops.rht_fused(self.gu[s.mlp:], 1, s.mlp, xd, gate=self.gu[:s.mlp], sign_in=L["down"].SU,
-                          hadk_bits=self.bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
+            ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
+                          hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
             self._matvec(L["down"], xd, self.y_h)
-            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=self.bits[self.kf_h],
+            self._all_reduce(self.y_h)
+            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
                           kfac=self.kf_h, scale=inv_h)
         # ---- final norm, lm_head, sampler (torch)
         h = (res_a + self.delta).float()

@@ -144,3 +144,51 @@ def test_legacy_entry_point_and_graph_capture():
     assert torch.equal(out2.view(-1), first.view(-1))
     with pytest.raises(RuntimeError):
         fn(out, compressed, x.float(), codebook)
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+def test_tensor_parallel_shards_equal_unsharded_layer(tp):
+    """Sum (row-parallel) / concatenation (column-parallel) of the per-rank results equals the unsharded
+    BitshiftLinear.forward with the matching rcp - all ranks emulated one after the other on one GPU."""
+    import math
+    from qtip_b200 import tp as tpmod
+    K = 2
+    tl = None
+    # ---- row-parallel: rcp = 1
+    m, n = 512, 6656                       # 6656 = 52 * 128; chunks keep the factor 52 down to tp = 8
+    lay = synth.make_layer(m, n, K, seed=500 + tp)
+    codes, SU, SV = t16(lay["codes"]), torch.from_numpy(lay["SU"]).to(DEV), torch.from_numpy(lay["SV"]).to(DEV)
+    tl = torch.from_numpy(lay["tlut"]).to(DEV)
+    x = torch.from_numpy(lay["x"]).to(DEV)
+    hl, kl = ops.get_hadK(n // tp)
+    hr, kr = ops.get_hadK(m)
+    hl = None if hl is None else hl.to(DEV)
+    bl = BitshiftLinear(16, 16, 16, K, 2, 9, "quantlut_sym", tlut=tl, has_kernel=True)
+    want = bl(x, codes, SU, SV, hl, None, kl, kr, 1, tp).float()
+    total = torch.zeros(1, m, device=DEV)
+    for r in range(tp):
+        c_r, su_r, sv_r, n_r = tpmod.shard_row_parallel(codes, SU, SV, m, n, K, r, tp)
+        xh = ops.rht(x[:, r * n_r:(r + 1) * n_r].contiguous(), sign_in=su_r.contiguous(), hadk_bits=ops.hadk_bits_for(hl, DEV),
+                     kfac=kl, transpose=True, scale=1 / (math.sqrt(n_r) * 32), out_dtype=torch.float16)
+        total += ops.decompress_matvec(c_r, xh, tl, K, m, n_r)
+    got = ops.rht(total, sign_out=SV * 32, scale=1 / math.sqrt(m), out_dtype=torch.float16).float()
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 1e-3
+    # ---- column-parallel: rcp = 2
+    m, n = 6656, 512
+    lay = synth.make_layer(m, n, K, seed=600 + tp)
+    codes, SU, SV = t16(lay["codes"]), torch.from_numpy(lay["SU"]).to(DEV), torch.from_numpy(lay["SV"]).to(DEV)
+    tl = torch.from_numpy(lay["tlut"]).to(DEV)
+    x = torch.from_numpy(lay["x"]).to(DEV)
+    hr, kr = ops.get_hadK(m // tp)
+    hr = None if hr is None else hr.to(DEV)
+    bl = BitshiftLinear(16, 16, 16, K, 2, 9, "quantlut_sym", tlut=tl, has_kernel=True)
+    want = bl(x, codes, SU, SV, None, hr, 1, kr, 2, tp).float()
+    xh = ops.rht(x, sign_in=SU, transpose=True, scale=1 / (math.sqrt(n) * 32), out_dtype=torch.float16)
+    outs = []
+    for r in range(tp):
+        c_r, su_r, sv_r, m_r = tpmod.shard_column_parallel(codes, SU, SV, m, n, K, r, tp)
+        y = ops.decompress_matvec(c_r.contiguous(), xh, tl, K, m_r, n)
+        outs.append(ops.rht(y, sign_out=sv_r.contiguous() * 32, hadk_bits=ops.hadk_bits_for(hr, DEV), kfac=kr,
+                            scale=1 / math.sqrt(m_r), out_dtype=torch.float16))
+    got = torch.cat(outs, dim=1).float()
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 1e-3
