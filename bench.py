@@ -98,6 +98,7 @@ def cpu_layer_seconds(repeats=3, K=2):
     import numpy as np
     import c_oracle as C
     from qtip_b200 import ops, synth
+    C.use_all_cores()
     times = []
     lays = {}
     for (m, n) in set(llama7b_linears()):
@@ -282,11 +283,13 @@ def run_gpu(args):
             "gpu_launches": model.n_launches_per_step * steps,
             "clocks": clocks.summary(),
         }
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
     if out is not None:
         print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        model.release_graph()  # graphs that captured NCCL kernels must go before the communicator
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
 
 
 def main():

@@ -36,6 +36,11 @@ def num_threads():
     return lib().qo_num_threads()
 
 
+def use_all_cores():
+    lib().qo_set_num_threads(os.cpu_count() or 1)
+    return num_threads()
+
+
 def float_to_half(x):
     x = np.ascontiguousarray(x, dtype=np.float32)
     y = np.empty(x.shape, dtype=np.uint16)

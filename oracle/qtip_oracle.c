@@ -64,6 +64,15 @@ void qo_init(void) {
     g_h2f_ready = 1;
 }
 
+/* launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline wants every host core */
+void qo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int qo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -239,6 +239,15 @@ class QtipLlama:
         self.token.copy_(tok); self.pos.copy_(pos)
         torch.cuda.synchronize(self.device)
 
+    def release_graph(self):
+        """Destroy the captured graph.  With tensor parallelism this must happen before the process group is
+        destroyed: NCCL does not tear a communicator down while a CUDA graph that captured its kernels is alive
+        (destroy_process_group blocks forever otherwise)."""
+        if self.graph is not None:
+            torch.cuda.synchronize(self.device)
+            self.graph.reset()
+            self.graph = None
+
     def reset(self):
         self.pos.zero_()
         self.cache_k.zero_(); self.cache_v.zero_()
