@@ -78,6 +78,40 @@ size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
 int qtip_decompress_matvec(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
                            int bs, void *workspace, size_t workspace_bytes, void *stream);
 
+/* One to four QTIP linears of the same shape in ONE launch (e.g. q/k/v, or gate/up), each optionally with
+ * its input-side and output-side transforms fused into the matvec kernel, i.e. the whole of
+ * BitshiftLinear.forward (lib/codebook/bitshift.py:428-472) for a decode step in one kernel:
+ *   input side  (in_raw != NULL; needs bs == 1 and n a power of two <= 16384): every CTA computes
+ *       x = fp16( H_n^T( sign_in * [silu(gate) *] [RMSNorm]( in_raw [+ residual] ) ) * in_scale )
+ *       itself; residual_out (if given) receives in_raw + residual; norm_weight / gate / residual optional.
+ *   matvec      y (bs, m) fp32 = x @ decode(codes)^T, always written.
+ *   output side (out != NULL; needs m a power of two <= 16384): the CTA that finishes last computes
+ *       out = sign_out * H_m(y) * out_scale  (fp16 or fp32).
+ * H is the unnormalised Walsh-Hadamard transform; fold n^-1/2, /32 and x32 into the scales as for qtip_rht.
+ * Either all descriptors of a call use the fused input side or none does.  Every descriptor needs its
+ * own zero-initialised workspace (qtip_matvec_workspace_bytes) and its own y. */
+typedef struct qtip_linear_desc {
+    float *y;
+    const void *codes;            /* kernel layout, K*m*n/8 bytes */
+    const void *tlut;             /* 512 x 2 fp16 */
+    const void *x;                /* (bs, n) fp16, used when in_raw == NULL */
+    void *workspace;
+    size_t workspace_bytes;
+    const void *in_raw;           /* (n) fp16 */
+    const void *residual;         /* (n) fp16 or NULL */
+    void *residual_out;           /* (n) fp16 or NULL; must not alias in_raw / residual */
+    const void *norm_weight;      /* (n) fp16 or NULL */
+    const void *gate;             /* (n) fp16 or NULL */
+    const void *sign_in;          /* (n) fp16 or NULL */
+    float in_scale;
+    float eps;
+    void *out;                    /* (bs, m) of out_dtype or NULL */
+    int out_dtype;
+    const float *sign_out;        /* (m) fp32 or NULL */
+    float out_scale;
+} qtip_linear_desc;
+int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream);
+
 /* qtip_decompress_matvec for callers that must not allocate device memory and have none to spare for a
  * workspace - a serving loop that froze its memory pool at start-up, a plug-in whose host owns every
  * allocation, code running where a cudaMalloc would synchronise the device.  (No counterpart in the

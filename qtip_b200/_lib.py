@@ -15,6 +15,14 @@ F16, F32 = 0, 1
 
 _vp, _i, _l, _sz, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t, ctypes.c_float
 
+class LinearDesc(ctypes.Structure):
+    """qtip_linear_desc of include/qtip_b200.h."""
+    _fields_ = [("y", _vp), ("codes", _vp), ("tlut", _vp), ("x", _vp), ("workspace", _vp), ("workspace_bytes", _sz),
+                ("in_raw", _vp), ("residual", _vp), ("residual_out", _vp), ("norm_weight", _vp), ("gate", _vp),
+                ("sign_in", _vp), ("in_scale", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("sign_out", _vp),
+                ("out_scale", _f)]
+
+
 # name -> (restype, argtypes); mirrors include/qtip_b200.h
 SIGNATURES = {
     "qtip_status_string": (ctypes.c_char_p, [_i]),
@@ -25,6 +33,7 @@ SIGNATURES = {
     "qtip_matvec_workspace_bytes": (_sz, [_i, _i, _i]),
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_decompress_matvec_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "qtip_linear_fused": (_i, [ctypes.POINTER(LinearDesc), _i, _i, _i, _i, _i, _vp]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,

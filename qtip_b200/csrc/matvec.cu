@@ -38,7 +38,7 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "common.cuh"
+#include "fwht.cuh"
 
 namespace qtip {
 namespace {
@@ -55,7 +55,7 @@ constexpr int kMaxBatch = 8;
 
 // ---- workspace layout (all offsets fixed, independent of the problem) -----------------------------
 // [0, 64 KiB)   ticket counters, one uint32 per 32-row block (m <= 524288); zero between calls
-// [64 KiB, +256) reserved
+// [64 KiB, +256) word 0: counter of finished CTAs (fused output transform); zero between calls
 // [.., end)     partial sums: [row block][contributor][8 batch x 32 rows] fp32
 constexpr size_t kCounterBytes = 64 * 1024;
 constexpr size_t kPartialOffset = kCounterBytes + 256;
@@ -80,10 +80,12 @@ struct Partition {
 // about as much time as streaming kTailBytes.
 constexpr long kTailBytes = 40 * 1024;
 
-Partition make_partition(int m, int n, int K) {
+// nprob problems of the same shape share one launch: each gets sm_count / nprob CTAs.
+Partition make_partition(int m, int n, int K, int nprob = 1) {
     static const int forced = [] { const char *e = getenv("QTIP_MATVEC_MODE"); return e ? atoi(e) : 0; }();
     Partition p;
-    const long mb = m >> 5, nb = n >> 5, B = mb * nb, sms = sm_count(), bb = 128 * K;
+    const long mb = m >> 5, nb = n >> 5, B = mb * nb, bb = 128 * K;
+    const long sms = sm_count() / nprob > 0 ? sm_count() / nprob : 1;
     const long g_stream = B < sms ? B : sms, g_rows = mb < sms ? mb : sms;
     const long cost_rows = ((mb + g_rows - 1) / g_rows) * nb * bb;
     const bool shared_rows = (B % g_stream) != 0 || ((B / g_stream) % nb) != 0;
@@ -129,6 +131,8 @@ struct SegmentIter {
 
 struct Shared {            // control block at the start of dynamic shared memory
     int is_last;
+    int pad_[7];
+    float warp_sums[32];   // scratch of block_sum
 };
 static_assert(sizeof(Shared) <= kCtrlBytes, "control block too large");
 
@@ -255,6 +259,32 @@ __device__ __forceinline__ void decode_block(const LaneCodes<K> &own, const Lane
     }
 }
 
+// One linear of a launch.  `in` / `ep` describe the optional transforms fused around the matvec.
+struct FusedIn {    // x_raw != nullptr: x = fp16( H^T( sign_in * [silu(gate) *] [RMSNorm](x_raw [+ residual]) ) * scale )
+    const __half *x_raw, *residual, *norm_weight, *gate, *sign_in;
+    __half *residual_out;
+    float scale, eps;
+};
+struct FusedOut {   // final != nullptr: final = sign_out * H(out) * scale, computed by the last CTA to finish
+    void *final;
+    const float *sign_out;
+    float scale;
+    int dtype;
+};
+struct MatvecProblem {
+    float *out;
+    const uint8_t *codes;
+    const __half *x;
+    const uint32_t *tlut;
+    uint8_t *workspace;
+    FusedIn in;
+    FusedOut ep;
+};
+constexpr int kMaxProblems = 4;
+struct MatvecBatch {
+    MatvecProblem p[kMaxProblems];
+};
+
 // Next lane's codes (wrap-around bits of the tail-biting stream: lane 31 takes lane 0's).
 template <int K>
 __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, int lane) {
@@ -268,22 +298,29 @@ __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, i
 // a block are one 16-byte load; otherwise they are read from global memory (L1-resident) per block.
 // DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
 // D:  software-pipeline depth - each warp keeps D of its blocks' codes in flight in registers.
+// blockIdx.y selects the problem of the batch (all problems have the same m, n, K, bs).
 template <int K, bool XS, bool DB, int D>
 __global__ void __launch_bounds__(kThreads, 1)
-    matvec_hyb_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
-                      const uint32_t *__restrict__ tlut, int m, int n, int bs, int kmax, int mode,
-                      uint8_t *__restrict__ workspace) {
+    matvec_hyb_kernel(const __grid_constant__ MatvecBatch batch, int m, int n, int bs, int kmax, int mode) {
     constexpr int kBlockBytes = 128 * K;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: control block | LUT | reduction buffer(s) [32][bs][32] fp32 | x (bs, n) fp16 permuted
+    // layout: control block | LUT | reduction buffer(s) [32][bs][32] fp32 | x (bs, n) fp16 permuted |
+    //         fp32 scratch of the fused input transform (n values, padded)
+    const MatvecProblem &P = batch.p[blockIdx.y];
+    float *__restrict__ out = P.out;
+    const uint8_t *__restrict__ codes = P.codes;
+    const __half *__restrict__ x = P.x;
+    const uint32_t *__restrict__ tlut = P.tlut;
     Shared *sh = reinterpret_cast<Shared *>(smem);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kCtrlBytes);
     const int red_floats = kConsumerWarps * 32 * bs;
     float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes);
     uint4 *xs = reinterpret_cast<uint4 *>(red + (DB ? 2 : 1) * red_floats);
+    float *fscratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xs) + (size_t)bs * n * 2);
 
-    unsigned *counters = reinterpret_cast<unsigned *>(workspace);
-    float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
+    unsigned *counters = reinterpret_cast<unsigned *>(P.workspace);
+    unsigned *done_counter = reinterpret_cast<unsigned *>(P.workspace + kCounterBytes);
+    float *partial = reinterpret_cast<float *>(P.workspace + kPartialOffset);
 
     const int nb = n >> 5, mb = m >> 5;
     const int G = gridDim.x;
@@ -321,11 +358,72 @@ __global__ void __launch_bounds__(kThreads, 1)
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
-        const uint32_t *xw = reinterpret_cast<const uint32_t *>(x);
-        const int words = bs * (n >> 1);
-        for (int i = threadIdx.x; i < words; i += kThreads) {
-            const int blk = i >> 4, w = i & 15;          // 16 words per 32-column block
-            reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = __ldg(xw + i);
+        if (P.in.x_raw) {
+            // fused input side (bs == 1, n a power of two): every CTA transforms the activation itself.
+            // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
+            // the whole prologue costs one L2 round trip, not one per array.
+            const FusedIn &I = P.in;
+            const int nvec = n >> 3;
+            float ss = 0.f;
+            for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
+                const size_t j = (size_t)vi * 8;
+                float v[8], rs[8], w[8], gt[8], sg[8];
+                load8_f16(I.x_raw, j, v);
+                if (I.residual) load8_f16(I.residual, j, rs);
+                if (I.norm_weight) load8_f16(I.norm_weight, j, w);
+                if (I.gate) load8_f16(I.gate, j, gt);
+                if (I.sign_in) load8_f16(I.sign_in, j, sg);
+                if (I.residual) {
+#pragma unroll
+                    for (int k = 0; k < 8; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));   // fp16 residual stream
+                    if (I.residual_out && blockIdx.x == 0) store8_f16(I.residual_out, j, v);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    ss += v[k] * v[k];
+                    // without a norm everything can be applied right away; with one the weight is folded in now
+                    // and the common factor r after the reduction: w * fp16(v * r) needs r first, so stash v
+                    if (!I.norm_weight) {
+                        if (I.gate) v[k] = swiglu_fp16(gt[k], v[k]);
+                        if (I.sign_in) v[k] *= sg[k];
+                    }
+                    fscratch[pad((int)j + k)] = v[k];
+                }
+            }
+            if (I.norm_weight) {
+                const float r = rsqrtf(block_sum(ss, sh->warp_sums) / (float)n + I.eps);
+                for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {   // each thread revisits its own values
+                    const size_t j = (size_t)vi * 8;
+                    float w[8], gt[8], sg[8];
+                    load8_f16(I.norm_weight, j, w);
+                    if (I.gate) load8_f16(I.gate, j, gt);
+                    if (I.sign_in) load8_f16(I.sign_in, j, sg);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        float v = fscratch[pad((int)j + k)];
+                        v = __half2float(__hmul(__float2half_rn(w[k]), __float2half_rn(v * r)));   // LlamaRMSNorm
+                        if (I.gate) v = swiglu_fp16(gt[k], v);
+                        if (I.sign_in) v *= sg[k];
+                        fscratch[pad((int)j + k)] = v;
+                    }
+                }
+            }
+            __syncthreads();
+            int p = 0;
+            while ((1 << p) < n) p++;
+            fwht_shared(fscratch, n, p);
+            for (int i = threadIdx.x; i < (n >> 1); i += kThreads) {
+                const int blk = i >> 4, w = i & 15;
+                const __half2 h = __floats2half2_rn(fscratch[pad(2 * i)] * I.scale, fscratch[pad(2 * i + 1)] * I.scale);
+                reinterpret_cast<__half2 *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = h;
+            }
+        } else {
+            const uint32_t *xw = reinterpret_cast<const uint32_t *>(x);
+            const int words = bs * (n >> 1);
+            for (int i = threadIdx.x; i < words; i += kThreads) {
+                const int blk = i >> 4, w = i & 15;          // 16 words per 32-column block
+                reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = __ldg(xw + i);
+            }
         }
     }
     __syncthreads();
@@ -390,6 +488,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         segno++;
         pos = npos;
         seg_end = nseg_end;
+    }
+
+    if (P.ep.final) {
+        // fused output side (m a power of two): the CTA that finishes last transforms the whole result
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) sh->is_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
+        __syncthreads();
+        if (sh->is_last) {
+            __threadfence();
+            float *f = reinterpret_cast<float *>(lut);   // the table is no longer needed
+            int p = 0;
+            while ((1 << p) < m) p++;
+            const int mvec = m >> 3;
+            for (int b = 0; b < bs; b++) {
+                for (int vi = threadIdx.x; vi < mvec; vi += kThreads) {
+                    const float4 *src = reinterpret_cast<const float4 *>(out + (size_t)b * m + (size_t)vi * 8);
+                    const float4 a = __ldcg(src), c = __ldcg(src + 1);
+                    const int j = vi * 8;
+                    f[pad(j)] = a.x; f[pad(j + 1)] = a.y; f[pad(j + 2)] = a.z; f[pad(j + 3)] = a.w;
+                    f[pad(j + 4)] = c.x; f[pad(j + 5)] = c.y; f[pad(j + 6)] = c.z; f[pad(j + 7)] = c.w;
+                }
+                __syncthreads();
+                fwht_shared(f, m, p);
+                for (int vi = threadIdx.x; vi < mvec; vi += kThreads) {
+                    const size_t j = (size_t)vi * 8;
+                    float y[8], sg[8];
+                    if (P.ep.sign_out) load8_f32(P.ep.sign_out, j, sg);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        y[k] = f[pad((int)j + k)] * P.ep.scale;
+                        if (P.ep.sign_out) y[k] *= sg[k];
+                    }
+                    if (P.ep.dtype == QTIP_F16) store8_f16(static_cast<__half *>(P.ep.final), (size_t)b * m + j, y);
+                    else store8_f32(static_cast<float *>(P.ep.final), (size_t)b * m + j, y);
+                }
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) *done_counter = 0;  // leave the workspace ready for the next call
+        }
     }
 }
 
@@ -485,8 +623,7 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
 }
 
 template <int K, bool XS, bool DB>
-int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
-                       uint8_t *workspace, int smem_total, cudaStream_t s) {
+int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
     constexpr int D = K == 2 ? 4 : 2;  // blocks in flight per warp: 32 warps x D x 128K bytes = 32 KiB per SM
     static bool attr_set[64] = {};
     int dev = 0;
@@ -496,9 +633,9 @@ int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const 
                                            kSmemLimit));
         attr_set[dev] = true;
     }
-    const Partition p = make_partition(m, n, K);
+    const Partition p = make_partition(m, n, K, nprob);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.grid);
+    cfg.gridDim = dim3(p.grid, nprob);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_total;
     cfg.stream = s;
@@ -507,26 +644,36 @@ int launch_hyb_variant(float *out, const uint8_t *codes, const __half *x, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D>, out, codes, x, tlut, m, n, bs, p.kmax, p.mode,
-                                     workspace));
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D>, batch, m, n, bs, p.kmax, p.mode));
     return check_launch();
+}
+
+// fused_in: the batch uses the fused input transform (needs x staged in shared memory plus fp32 scratch)
+template <int K>
+int launch_hyb_batch(const MatvecBatch &batch, int nprob, int m, int n, int bs, bool fused_in, cudaStream_t s) {
+    // shared memory: control + table are fixed; then the reduction buffer(s) and, when it fits, x
+    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
+    const int x_bytes = bs * n * 2;
+    const int scratch_bytes = fused_in ? (n + (n >> 5) + 8) * (int)sizeof(float) : 0;
+    const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
+    const bool db = 2 * red_bytes <= avail / 2;
+    const int fixed = (db ? 2 : 1) * red_bytes;
+    const bool xs = fixed + x_bytes + scratch_bytes <= avail;
+    if (fused_in && !xs) return QTIP_ERR_BAD_SHAPE;
+    const int smem_total = kCtrlBytes + kLutBytes + fixed + (xs ? x_bytes + scratch_bytes : 0);
+    if (xs && db) return launch_hyb_variant<K, true, true>(batch, nprob, m, n, bs, smem_total, s);
+    if (xs) return launch_hyb_variant<K, true, false>(batch, nprob, m, n, bs, smem_total, s);
+    if (db) return launch_hyb_variant<K, false, true>(batch, nprob, m, n, bs, smem_total, s);
+    return launch_hyb_variant<K, false, false>(batch, nprob, m, n, bs, smem_total, s);
 }
 
 template <int K>
 int launch_hyb(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs,
                uint8_t *workspace, cudaStream_t s) {
-    // shared memory: control + table are fixed; then the reduction buffer(s) and, when it fits, x
-    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
-    const int x_bytes = bs * n * 2;
-    const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
-    const bool db = 2 * red_bytes <= avail / 2;
-    const int fixed = (db ? 2 : 1) * red_bytes;
-    const bool xs = fixed + x_bytes <= avail;
-    const int smem_total = kCtrlBytes + kLutBytes + fixed + (xs ? x_bytes : 0);
-    if (xs && db) return launch_hyb_variant<K, true, true>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
-    if (xs) return launch_hyb_variant<K, true, false>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
-    if (db) return launch_hyb_variant<K, false, true>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
-    return launch_hyb_variant<K, false, false>(out, codes, x, tlut, m, n, bs, workspace, smem_total, s);
+    MatvecBatch batch = {};
+    batch.p[0].out = out; batch.p[0].codes = codes; batch.p[0].x = x; batch.p[0].tlut = tlut;
+    batch.p[0].workspace = workspace;
+    return launch_hyb_batch<K>(batch, 1, m, n, bs, false, s);
 }
 
 }  // namespace
@@ -582,6 +729,49 @@ extern "C" int qtip_decompress_matvec_plain(float *out, const void *codes, const
         matvec_plain_kernel<QTIP_CODE_1MAD><<<p.grid, kPlainWarps * 32, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax,
                                                                                  p.mode, ws);
     return check_launch();
+}
+
+extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream) {
+    if (!descs || count < 1 || count > kMaxProblems) return QTIP_ERR_BAD_ARG;
+    MatvecBatch batch = {};
+    bool fused_in = false;
+    for (int i = 0; i < count; i++) {
+        const qtip_linear_desc &d = descs[i];
+        if (!d.tlut) return QTIP_ERR_BAD_ARG;
+        const bool fin = d.in_raw != nullptr, fout = d.out != nullptr;
+        if (i > 0 && fin != fused_in) return QTIP_ERR_BAD_ARG;   // all or none: the shared-memory layout is per launch
+        fused_in = fin;
+        const void *x = fin ? d.in_raw : d.x;
+        int st = check_common(d.y, d.codes, x, K, m, n, bs, d.workspace, d.workspace_bytes);
+        if (st != QTIP_OK) return st;
+        if (!aligned(d.tlut, 4)) return QTIP_ERR_ALIGNMENT;
+        if (fin && (bs != 1 || (n & (n - 1)) || n > 16384)) return QTIP_ERR_BAD_SHAPE;
+        if (fout && ((m & (m - 1)) || m > 16384)) return QTIP_ERR_BAD_SHAPE;
+        if (fout && d.out_dtype != QTIP_F16 && d.out_dtype != QTIP_F32) return QTIP_ERR_BAD_ARG;
+        {
+            const void *vecs[] = {d.in_raw, d.residual, d.residual_out, d.norm_weight, d.gate, d.sign_in, d.out, d.sign_out,
+                                  (fin || fout) ? (const void *)d.y : nullptr};
+            for (const void *q : vecs)
+                if (q && !aligned(q, 16)) return QTIP_ERR_ALIGNMENT;
+        }
+        if (d.residual_out && (d.residual_out == d.in_raw || d.residual_out == d.residual)) return QTIP_ERR_BAD_ARG;
+        for (int j = 0; j < i; j++)
+            if (descs[j].workspace == d.workspace || descs[j].y == d.y) return QTIP_ERR_BAD_ARG;
+        MatvecProblem &P = batch.p[i];
+        P.out = d.y; P.codes = static_cast<const uint8_t *>(d.codes); P.x = static_cast<const __half *>(d.x);
+        P.tlut = static_cast<const uint32_t *>(d.tlut); P.workspace = static_cast<uint8_t *>(d.workspace);
+        if (fin) {
+            P.in.x_raw = static_cast<const __half *>(d.in_raw); P.in.residual = static_cast<const __half *>(d.residual);
+            P.in.residual_out = static_cast<__half *>(d.residual_out);
+            P.in.norm_weight = static_cast<const __half *>(d.norm_weight); P.in.gate = static_cast<const __half *>(d.gate);
+            P.in.sign_in = static_cast<const __half *>(d.sign_in); P.in.scale = d.in_scale; P.in.eps = d.eps;
+        }
+        if (fout) { P.ep.final = d.out; P.ep.sign_out = d.sign_out; P.ep.scale = d.out_scale; P.ep.dtype = d.out_dtype; }
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 2) return launch_hyb_batch<2>(batch, count, m, n, bs, fused_in, s);
+    if (K == 3) return launch_hyb_batch<3>(batch, count, m, n, bs, fused_in, s);
+    return launch_hyb_batch<4>(batch, count, m, n, bs, fused_in, s);
 }
 
 // ---- allocation-free variant ------------------------------------------------------------------------------

@@ -19,12 +19,12 @@
 //
 // Launched with programmatic stream serialization: the hadK sign table (weights) is expanded
 // before griddepcontrol.wait, activations are touched after it.
-#include "common.cuh"
+#include "fwht.cuh"
 
 namespace qtip {
 namespace {
 
-constexpr int kRhtThreads = 512;
+constexpr int kRhtThreads = 1024;
 constexpr int kRowsPerCta = 16;  // hadK output rows per CTA
 
 struct RhtArgs {
@@ -37,89 +37,18 @@ struct RhtArgs {
     float scale, eps;
 };
 
-// Shared-memory index with one pad word per 32: a thread that walks 16 consecutive values (first
-// butterfly pass) then hits 32 different banks across a warp instead of 2.
-__device__ __forceinline__ int pad(int i) { return i + (i >> 5); }
-
-template <int R>
-__device__ __forceinline__ void butterfly_pass(float *v, int n, int b) {
-    constexpr int E = 1 << R;
-    const int groups = n >> R;
-    for (int gidx = threadIdx.x; gidx < groups; gidx += blockDim.x) {
-        const int lo = gidx & ((1 << b) - 1), hi = gidx >> b;
-        const int base = (hi << (b + R)) | lo;
-        float e[E];
-#pragma unroll
-        for (int k = 0; k < E; k++) e[k] = v[pad(base + (k << b))];
-#pragma unroll
-        for (int s = 0; s < R; s++) {
-#pragma unroll
-            for (int k = 0; k < E; k++) {
-                if (!(k & (1 << s))) {
-                    float a0 = e[k], a1 = e[k | (1 << s)];
-                    e[k] = a0 + a1;
-                    e[k | (1 << s)] = a0 - a1;
-                }
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < E; k++) v[pad(base + (k << b))] = e[k];
-    }
-}
-
 __device__ __forceinline__ float load_elem(const void *p, int dtype, size_t i) {
     return dtype == QTIP_F16 ? __half2float(static_cast<const __half *>(p)[i]) : static_cast<const float *>(p)[i];
 }
 
 // 8 consecutive elements starting at element i (i % 8 == 0, base pointers 16-byte aligned)
 __device__ __forceinline__ void load8(const void *p, int dtype, size_t i, float (&o)[8]) {
-    if (dtype == QTIP_F16) {
-        const uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p) + i);
-        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; k++) { o[2 * k] = __low2float(h[k]); o[2 * k + 1] = __high2float(h[k]); }
-    } else {
-        const float4 a = *reinterpret_cast<const float4 *>(static_cast<const float *>(p) + i);
-        const float4 b = *reinterpret_cast<const float4 *>(static_cast<const float *>(p) + i + 4);
-        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-    }
+    if (dtype == QTIP_F16) load8_f16(static_cast<const __half *>(p), i, o);
+    else load8_f32(static_cast<const float *>(p), i, o);
 }
-
 __device__ __forceinline__ void store8(void *p, int dtype, size_t i, const float (&o)[8]) {
-    if (dtype == QTIP_F16) {
-        uint4 raw;
-        __half2 *h = reinterpret_cast<__half2 *>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; k++) h[k] = __floats2half2_rn(o[2 * k], o[2 * k + 1]);
-        *reinterpret_cast<uint4 *>(static_cast<__half *>(p) + i) = raw;
-    } else {
-        *reinterpret_cast<float4 *>(static_cast<float *>(p) + i) = make_float4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<float4 *>(static_cast<float *>(p) + i + 4) = make_float4(o[4], o[5], o[6], o[7]);
-    }
-}
-
-__device__ __forceinline__ float block_sum(float x, float *scratch) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(kFullMask, x, o);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();
-    if (lane == 0) scratch[warp] = x;
-    __syncthreads();
-    float t = 0.f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += scratch[w];
-    return t;
-}
-
-// The fused prologue applied to one value (everything except the RMS statistic).
-__device__ __forceinline__ float gate_and_sign(const RhtArgs &a, float x, size_t in_idx, size_t sign_idx) {
-    if (a.gate) {
-        // SwiGLU: silu(gate) in fp16 precision, product rounded to fp16 (the activations are fp16 tensors)
-        const float gt = __half2float(a.gate[in_idx]);
-        const __half sg = __float2half_rn(gt / (1.0f + __expf(-gt)));
-        x = __half2float(__hmul(sg, __float2half_rn(x)));
-    }
-    if (a.sign_in) x *= load_elem(a.sign_in, a.sign_in_dtype, sign_idx);
-    return x;
+    if (dtype == QTIP_F16) store8_f16(static_cast<__half *>(p), i, o);
+    else store8_f32(static_cast<float *>(p), i, o);
 }
 
 __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
@@ -128,50 +57,75 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     float *v = sm;                            // n values, padded (see pad())
     float *hs = sm + pad(n) + 1;              // kfac x kRowsPerCta signs (+-1.0f), [k][row], only when kfac > 1
     hs = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(hs) + 15) & ~(uintptr_t)15);
-    float *scratch = hs + (kfac > 1 ? kRowsPerCta * kfac : 0);  // 32 floats
+    float *scratch = hs + (kfac > 1 ? kRowsPerCta * kfac : 0);  // 32 floats (block_sum)
+    uint32_t *bits = reinterpret_cast<uint32_t *>(scratch + 32);  // the packed hadK matrix, kfac * ceil(kfac/32) words
     const long row = blockIdx.y;
     const size_t sign_off = (size_t)(row % a.sign_rep) * n;
     const size_t in_off = (size_t)row * a.in_row_stride, out_off = (size_t)row * n;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
 
     const int i0 = blockIdx.x * kRowsPerCta;
     const int rows_here = min(kRowsPerCta, kfac - i0);
     if (kfac > 1) {
-        // hs[k][il] = hadK[i0+il][k], or hadK[k][i0+il] for the transposed (input-side) transform
+        // one coalesced read of the bit matrix, then hs[k][il] = hadK[i0+il][k]
+        // (hadK[k][i0+il] for the transposed, input-side transform)
         const int wpr = (kfac + 31) >> 5;
-        for (int il = warp; il < kRowsPerCta; il += nwarps)
-            for (int k = lane; k < kfac; k += 32) {
-                float sgn = 0.f;
-                if (il < rows_here) {
-                    const int rr = a.transpose ? k : (i0 + il), cc = a.transpose ? (i0 + il) : k;
-                    sgn = ((a.hadk_bits[rr * wpr + (cc >> 5)] >> (cc & 31)) & 1u) ? 1.0f : -1.0f;
-                }
-                hs[k * kRowsPerCta + il] = sgn;
+        for (int i = threadIdx.x; i < kfac * wpr; i += blockDim.x) bits[i] = a.hadk_bits[i];
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kRowsPerCta * kfac; idx += blockDim.x) {
+            const int k = idx >> 4, il = idx & (kRowsPerCta - 1);
+            float sgn = 0.f;
+            if (il < rows_here) {
+                const int rr = a.transpose ? k : (i0 + il), cc = a.transpose ? (i0 + il) : k;
+                sgn = ((bits[rr * wpr + (cc >> 5)] >> (cc & 31)) & 1u) ? 1.0f : -1.0f;
             }
+            hs[idx] = sgn;
+        }
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool vec = a.vec_ok;
+    const bool write_res = a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0);
     float ss = 0.f;
     if (vec) {
+        // a thread owns 8 consecutive values; all operand vectors are requested before any is used
         for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
-            float x[8];
+            float x[8], rs[8], gt[8], sg[8];
             load8(a.in, a.in_dtype, in_off + j, x);
+            if (a.residual) load8_f16(a.residual, in_off + j, rs);
+            if (a.gate && !a.norm_weight) load8_f16(a.gate, in_off + j, gt);
+            if (a.sign_in && !a.norm_weight) load8(a.sign_in, a.sign_in_dtype, sign_off + j, sg);
             if (a.residual) {
-                float r[8];
-                load8(a.residual, QTIP_F16, in_off + j, r);
                 // the residual stream is fp16: the sum is rounded to fp16 as an fp16 add would
 #pragma unroll
-                for (int k = 0; k < 8; k++) x[k] = __half2float(__float2half_rn(x[k] + r[k]));
-                if (a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0))
-                    store8(a.residual_out, QTIP_F16, in_off + j, x);
+                for (int k = 0; k < 8; k++) x[k] = __half2float(__float2half_rn(x[k] + rs[k]));
+                if (write_res) store8_f16(a.residual_out, in_off + j, x);
             }
 #pragma unroll
             for (int k = 0; k < 8; k++) {
                 ss += x[k] * x[k];
-                if (!a.norm_weight) x[k] = gate_and_sign(a, x[k], in_off + j + k, sign_off + j + k);
+                if (!a.norm_weight) {
+                    if (a.gate) x[k] = swiglu_fp16(gt[k], x[k]);
+                    if (a.sign_in) x[k] *= sg[k];
+                }
                 v[pad(j + k)] = x[k];
+            }
+        }
+        if (a.norm_weight) {
+            // LlamaRMSNorm: fp32 statistics, normalised value rounded to fp16, then times the fp16 weight
+            const float r = rsqrtf(block_sum(ss, scratch) / (float)n + a.eps);
+            for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
+                float w[8], gt[8], sg[8];
+                load8_f16(a.norm_weight, j, w);
+                if (a.gate) load8_f16(a.gate, in_off + j, gt);
+                if (a.sign_in) load8(a.sign_in, a.sign_in_dtype, sign_off + j, sg);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    float x = __half2float(__hmul(__float2half_rn(w[k]), __float2half_rn(v[pad(j + k)] * r)));
+                    if (a.gate) x = swiglu_fp16(gt[k], x);
+                    if (a.sign_in) x *= sg[k];
+                    v[pad(j + k)] = x;
+                }
             }
         }
     } else {
@@ -179,47 +133,37 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
             float x = load_elem(a.in, a.in_dtype, in_off + j);
             if (a.residual) {
                 x = __half2float(__float2half_rn(x + __half2float(a.residual[in_off + j])));
-                if (a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0))
-                    a.residual_out[in_off + j] = __float2half_rn(x);
+                if (write_res) a.residual_out[in_off + j] = __float2half_rn(x);
             }
             ss += x * x;
-            if (!a.norm_weight) x = gate_and_sign(a, x, in_off + j, sign_off + j);
             v[pad(j)] = x;
         }
-    }
-    if (a.norm_weight) {
-        // LlamaRMSNorm: fp32 statistics, normalised value rounded to fp16, then times the fp16 weight
-        const float r = rsqrtf(block_sum(ss, scratch) / (float)n + a.eps);
+        float r = 1.f;
+        if (a.norm_weight) r = rsqrtf(block_sum(ss, scratch) / (float)n + a.eps);
         for (int j = threadIdx.x; j < n; j += blockDim.x) {
-            const __half hn = __float2half_rn(v[pad(j)] * r);
-            v[pad(j)] = gate_and_sign(a, __half2float(__hmul(a.norm_weight[j], hn)), in_off + j, sign_off + j);
+            float x = v[pad(j)];
+            if (a.norm_weight) x = __half2float(__hmul(a.norm_weight[j], __float2half_rn(x * r)));
+            if (a.gate) x = swiglu_fp16(__half2float(a.gate[in_off + j]), x);
+            if (a.sign_in) x *= load_elem(a.sign_in, a.sign_in_dtype, sign_off + j);
+            v[pad(j)] = x;
         }
     }
     __syncthreads();
 
     const int p = a.p;
-    for (int b = 0; b < p;) {
-        const int r = (p - b) >= 4 ? 4 : (p - b);
-        switch (r) {
-            case 4: butterfly_pass<4>(v, n, b); break;
-            case 3: butterfly_pass<3>(v, n, b); break;
-            case 2: butterfly_pass<2>(v, n, b); break;
-            default: butterfly_pass<1>(v, n, b); break;
-        }
-        b += r;
-        __syncthreads();
-    }
+    fwht_shared(v, n, p);
 
     const int len = 1 << p;
     const float scale = a.scale;
     if (kfac == 1) {
         if (vec) {
             for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
-                float y[8];
+                float y[8], sg[8];
+                if (a.sign_out) load8_f32(a.sign_out, sign_off + j, sg);
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     y[k] = v[pad(j + k)] * scale;
-                    if (a.sign_out) y[k] *= a.sign_out[sign_off + j + k];
+                    if (a.sign_out) y[k] *= sg[k];
                 }
                 store8(a.out, a.out_dtype, out_off + j, y);
             }
@@ -238,6 +182,13 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     const int items = (kRowsPerCta / 4) * len;
     for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
         const int j = idx & (len - 1), il = (idx >> p) * 4;
+        // sign_out of the 4 outputs, requested before the long loop
+        float so[4] = {1.f, 1.f, 1.f, 1.f};
+        if (a.sign_out) {
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+                if (il + r < rows_here) so[r] = a.sign_out[sign_off + (size_t)(i0 + il + r) * len + j];
+        }
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
         for (int k = 0; k < kfac; k++) {
@@ -250,8 +201,7 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
         for (int r = 0; r < 4; r++) {
             if (il + r < rows_here) {
                 const size_t o = (size_t)(i0 + il + r) * len + j;
-                float y = acc[r] * scale;
-                if (a.sign_out) y *= a.sign_out[sign_off + o];
+                const float y = acc[r] * scale * so[r];
                 if (a.out_dtype == QTIP_F16) static_cast<__half *>(a.out)[out_off + o] = __float2half_rn(y);
                 else static_cast<float *>(a.out)[out_off + o] = y;
             }
@@ -271,9 +221,10 @@ int launch_rht(RhtArgs a, long rows, void *stream) {
     int p = 0;
     while ((1 << p) < len) p++;
     a.p = p;
-    const size_t smem = ((size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)kRowsPerCta * a.kfac : 0) + 32) * sizeof(float);
+    const size_t smem = ((size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)kRowsPerCta * a.kfac : 0) + 32 +
+                         (a.kfac > 1 ? (size_t)a.kfac * ((a.kfac + 31) / 32) : 0)) * sizeof(float);
     {
-        const void *ptrs[] = {a.out, a.in, a.residual, a.residual_out, a.gate};
+        const void *ptrs[] = {a.out, a.in, a.residual, a.residual_out, a.gate, a.sign_in, a.sign_out, a.norm_weight};
         bool ok = (a.n % 8 == 0) && (a.in_row_stride % 8 == 0);
         for (const void *q : ptrs) ok = ok && aligned(q, 16);
         a.vec_ok = ok ? 1 : 0;

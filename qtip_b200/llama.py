@@ -3,14 +3,15 @@
 This is the measurement harness for end-to-end decode speed: a random-init model of a given shape
 (`LlamaShape`), a static KV cache, and one CUDA graph per decode step, replayed once per token
 (upstream: eval/interactive_gen.py:42-85 with model/llama.py; the graph capture follows the pattern
-of lib/utils/graph_wrapper.py:16-47 instead of torch.compile).  Inside the graph a decoder layer is
-17 launches of this library's kernels:
-    RHT-in for q,k,v (one launch, fused residual add + RMSNorm)   3 fused decode-matvecs   RHT-out (one launch)
+of lib/utils/graph_wrapper.py:16-47 instead of torch.compile).  Inside the graph a decoder layer of the
+Llama-2-7B shape is 8 launches of this library's kernels:
+    q,k,v in one launch (residual add, RMSNorm, input and output transforms fused)
     RoPE + KV append     single-query attention
-    RHT-in(o)  matvec  RHT-out
-    RHT-in for gate,up (one launch, fused residual add + RMSNorm)  2 matvecs  RHT-out (one launch)
-    RHT-in(down) with the SwiGLU product fused   matvec   RHT-out
-The embedding lookup, the final norm, the fp16 lm_head and the sampler are plain torch ops.
+    o_proj in one launch (both transforms fused)
+    gate,up in one launch (residual add, RMSNorm, input transform fused)   their output transform (11008 = 172*64)
+    input transform of down_proj with the SwiGLU product fused             down_proj (output transform fused)
+Widths that are not powers of two, and tensor-parallel row-parallel layers (all-reduce between matvec and
+output transform), fall back to separate transform launches.  The embedding lookup, the final norm, the fp16 lm_head and the sampler are plain torch ops.
 """
 import math
 from dataclasses import dataclass
@@ -128,8 +129,13 @@ class QtipLlama:
         need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
                    for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        self.workspaces = [self.workspace] + [torch.zeros(need, dtype=torch.uint8, device=dev) for _ in range(2)]
+        pow2 = lambda d: d & (d - 1) == 0  # noqa: E731
+        # which transforms can ride inside the matvec launch (powers of two only; see qtip_linear_fused)
+        self.fuse_in_h, self.fuse_in_hl, self.fuse_in_m = pow2(s.hidden), pow2(H), pow2(MLP)
+        self.fuse_out_h, self.fuse_out_hl, self.fuse_out_kv, self.fuse_out_m = pow2(s.hidden), pow2(H), pow2(KV), pow2(MLP)
         self.graph = None
-        self.n_launches_per_step = (17 if H == KV and self.kf_hl == self.kf_kv else 18) * s.n_layers
+        self.n_launches_per_step = None   # counted while the step runs (library launches only)
 
     # -- one linear: the three launches ------------------------------------------------------------
     def _matvec(self, lin, xh, y):
@@ -140,6 +146,25 @@ class QtipLlama:
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 
+    def _linears(self, lins, xs_or_raw, ys, n, m, *, fused_in=None, outs=None, sign_outs=None, out_scale=1.0):
+        """One launch for the same-shape linears `lins`.  fused_in: dict(in_raw, residual, residual_out, norm_weight,
+        gate, sign_ins, in_scale) or None (then xs_or_raw holds the transformed fp16 inputs).  outs: fused output side."""
+        descs = []
+        for i, lin in enumerate(lins):
+            d = dict(y=ys[i], codes=lin.codes, tlut=lin.tlut, workspace=self.workspaces[i])
+            if fused_in is None:
+                d["x"] = xs_or_raw[i]
+            else:
+                d.update(in_raw=fused_in["in_raw"], residual=fused_in.get("residual"), norm_weight=fused_in.get("norm_weight"),
+                         gate=fused_in.get("gate"), sign_in=fused_in["sign_ins"][i], in_scale=fused_in["in_scale"],
+                         eps=self.shape.rms_eps)
+                if i == 0:
+                    d["residual_out"] = fused_in.get("residual_out")
+            if outs is not None:
+                d.update(out=outs[i], sign_out=sign_outs[i], out_scale=out_scale)
+            descs.append(d)
+        ops.linear_fused(descs, lins[0].K, m, n, 1)
+
     def step(self):
         """One decode step on the static buffers: token -> next_token, pos += 1.  Capturable."""
         s = self.shape
@@ -149,59 +174,92 @@ class QtipLlama:
         self.delta.zero_()
         inv_h, inv_hl, inv_m, inv_kv = (1 / math.sqrt(d) for d in (s.hidden, H, MLP, KV))
         bits = self.bits
+        tp1 = self.tp == 1
+        y_q, y_k, y_v = self.y_qkv[:H], self.y_qkv[H:H + KV], self.y_qkv[H + KV:]
+        q, k, v = self.qkv[:H], self.qkv[H:H + KV], self.qkv[H + KV:]
         for li, L in enumerate(self.layers):
             # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v (column-parallel)
-            xh = self.xh_qkv
-            ops.rht_fused(self.delta, 3, s.hidden, xh, in_row_stride=0, residual=res_a, residual_out=res_b,
-                          norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=bits[self.kf_h],
-                          kfac=self.kf_h, transpose=True, scale=inv_h / 32)
-            self._matvec(L["q"], xh[0], self.y_qkv[:H])
-            self._matvec(L["k"], xh[1], self.y_qkv[H:H + KV])
-            self._matvec(L["v"], xh[2], self.y_qkv[H + KV:])
-            if H == KV and self.kf_hl == self.kf_kv:
-                sv = L.get("SV_qkv")
-                if sv is None:
-                    sv = L["SV_qkv"] = torch.cat([L["q"].SV32, L["k"].SV32, L["v"].SV32]).contiguous()
-                ops.rht_fused(self.y_qkv, 3, H, self.qkv, sign_out=sv, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
-                              scale=inv_hl)
+            if self.fuse_in_h and self.fuse_out_hl and self.fuse_out_kv:
+                fin = dict(in_raw=self.delta, residual=res_a, residual_out=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32)
+                if H == KV:
+                    self._linears([L["q"], L["k"], L["v"]], None, [y_q, y_k, y_v], s.hidden, H,
+                                  fused_in=dict(fin, sign_ins=[L["q"].SU, L["k"].SU, L["v"].SU]), outs=[q, k, v],
+                                  sign_outs=[L["q"].SV32, L["k"].SV32, L["v"].SV32], out_scale=inv_hl)
+                else:
+                    self._linears([L["q"]], None, [y_q], s.hidden, H, fused_in=dict(fin, sign_ins=[L["q"].SU]), outs=[q],
+                                  sign_outs=[L["q"].SV32], out_scale=inv_hl)
+                    fin2 = dict(in_raw=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32, sign_ins=[L["k"].SU, L["v"].SU])
+                    self._linears([L["k"], L["v"]], None, [y_k, y_v], s.hidden, KV, fused_in=fin2, outs=[k, v],
+                                  sign_outs=[L["k"].SV32, L["v"].SV32], out_scale=inv_kv)
             else:
-                ops.rht_fused(self.y_qkv[:H], 1, H, self.qkv[:H], sign_out=L["q"].SV32, hadk_bits=bits[self.kf_hl],
-                              kfac=self.kf_hl, scale=inv_hl)
+                xh = self.xh_qkv
+                ops.rht_fused(self.delta, 3, s.hidden, xh, in_row_stride=0, residual=res_a, residual_out=res_b,
+                              norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=bits[self.kf_h],
+                              kfac=self.kf_h, transpose=True, scale=inv_h / 32)
+                self._matvec(L["q"], xh[0], y_q)
+                self._matvec(L["k"], xh[1], y_k)
+                self._matvec(L["v"], xh[2], y_v)
+                ops.rht_fused(y_q, 1, H, q, sign_out=L["q"].SV32, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl, scale=inv_hl)
                 sv = L.get("SV_kv")
                 if sv is None:
                     sv = L["SV_kv"] = torch.cat([L["k"].SV32, L["v"].SV32]).contiguous()
                 ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=bits[self.kf_kv],
                               kfac=self.kf_kv, scale=inv_kv)
-            q, k, v = self.qkv[:H], self.qkv[H:H + KV], self.qkv[H + KV:]
             ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
                                s.head_dim, s.rope_theta)
             ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
                             s.head_dim)
             # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
-            xo = self.xh_o
-            ops.rht_fused(self.attn, 1, H, xo, sign_in=L["o"].SU, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
-                          transpose=True, scale=inv_hl / 32)
-            self._matvec(L["o"], xo, self.y_h)
-            self._all_reduce(self.y_h)
-            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=bits[self.kf_h],
-                          kfac=self.kf_h, scale=inv_h)
+            fuse_out = tp1 and self.fuse_out_h
+            if self.fuse_in_hl:
+                self._linears([L["o"]], None, [self.y_h], H, s.hidden,
+                              fused_in=dict(in_raw=self.attn, sign_ins=[L["o"].SU], in_scale=inv_hl / 32),
+                              outs=[self.delta] if fuse_out else None, sign_outs=[L["o"].SV32], out_scale=inv_h)
+            else:
+                ops.rht_fused(self.attn, 1, H, self.xh_o, sign_in=L["o"].SU, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
+                              transpose=True, scale=inv_hl / 32)
+                self._linears([L["o"]], [self.xh_o], [self.y_h], H, s.hidden, outs=[self.delta] if fuse_out else None,
+                              sign_outs=[L["o"].SV32], out_scale=inv_h)
+            if not fuse_out:
+                self._all_reduce(self.y_h)
+                ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=bits[self.kf_h],
+                              kfac=self.kf_h, scale=inv_h)
             # ---- MLP block: res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up (column-parallel)
-            xg = self.xh_gu
-            ops.rht_fused(self.delta, 2, s.hidden, xg, in_row_stride=0, residual=res_b, residual_out=res_a,
-                          norm_weight=L["ln2"], eps=s.rms_eps, sign_in=L["SU_gu"], hadk_bits=bits[self.kf_h],
-                          kfac=self.kf_h, transpose=True, scale=inv_h / 32)
-            self._matvec(L["gate"], xg[0], self.y_gu[:MLP])
-            self._matvec(L["up"], xg[1], self.y_gu[MLP:])
-            ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
-                          kfac=self.kf_m, scale=inv_m)
+            y_g, y_u = self.y_gu[:MLP], self.y_gu[MLP:]
+            if self.fuse_in_h:
+                fin = dict(in_raw=self.delta, residual=res_b, residual_out=res_a, norm_weight=L["ln2"], in_scale=inv_h / 32,
+                           sign_ins=[L["gate"].SU, L["up"].SU])
+                fo = self.fuse_out_m
+                self._linears([L["gate"], L["up"]], None, [y_g, y_u], s.hidden, MLP, fused_in=fin,
+                              outs=[self.gu[:MLP], self.gu[MLP:]] if fo else None,
+                              sign_outs=[L["gate"].SV32, L["up"].SV32], out_scale=inv_m)
+            else:
+                fo = False
+                xg = self.xh_gu
+                ops.rht_fused(self.delta, 2, s.hidden, xg, in_row_stride=0, residual=res_b, residual_out=res_a,
+                              norm_weight=L["ln2"], eps=s.rms_eps, sign_in=L["SU_gu"], hadk_bits=bits[self.kf_h],
+                              kfac=self.kf_h, transpose=True, scale=inv_h / 32)
+                self._matvec(L["gate"], xg[0], y_g)
+                self._matvec(L["up"], xg[1], y_u)
+            if not fo:
+                ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
+                              kfac=self.kf_m, scale=inv_m)
             # ---- down_proj (row-parallel), input silu(gate) * up
-            xd = self.xh_d
-            ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
-                          hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
-            self._matvec(L["down"], xd, self.y_h)
-            self._all_reduce(self.y_h)
-            ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
-                          kfac=self.kf_h, scale=inv_h)
+            fuse_out = tp1 and self.fuse_out_h
+            if self.fuse_in_m:
+                self._linears([L["down"]], None, [self.y_h], MLP, s.hidden,
+                              fused_in=dict(in_raw=self.gu[MLP:], gate=self.gu[:MLP], sign_ins=[L["down"].SU], in_scale=inv_m / 32),
+                              outs=[self.delta] if fuse_out else None, sign_outs=[L["down"].SV32], out_scale=inv_h)
+            else:
+                xd = self.xh_d
+                ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
+                              hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
+                self._linears([L["down"]], [xd], [self.y_h], MLP, s.hidden, outs=[self.delta] if fuse_out else None,
+                              sign_outs=[L["down"].SV32], out_scale=inv_h)
+            if not fuse_out:
+                self._all_reduce(self.y_h)
+                ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
+                              kfac=self.kf_h, scale=inv_h)
         # ---- final norm, lm_head, sampler (torch)
         h = (res_a + self.delta).float()
         h = (h * torch.rsqrt(h.pow(2).mean() + s.rms_eps)).half() * self.ln_f
@@ -229,7 +287,9 @@ class QtipLlama:
         with torch.cuda.stream(stream):
             self.step()
             self.token.copy_(tok); self.pos.copy_(pos)
+            before = ops.launch_count
             self.step()
+            self.n_launches_per_step = ops.launch_count - before
             self.token.copy_(tok); self.pos.copy_(pos)
             stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()

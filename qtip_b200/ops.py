@@ -15,6 +15,7 @@ from ._lib import CODE_1MAD, CODE_3INST, CODE_HYB, F16, F32  # noqa: F401
 CODE_IDS = {"quantlut_sym": CODE_HYB, "hyb": CODE_HYB, "3inst": CODE_3INST, "1mad": CODE_1MAD}
 HAD_FACTORS = (172, 156, 140, 124, 116, 108, 60, 52, 36, 28, 20, 12)
 MAX_MATVEC_BATCH = 8
+launch_count = 0   # kernel launches issued through this module (bench.py reports it)
 
 
 def _stream():
@@ -127,6 +128,8 @@ def decode_hyb(codes, tlut, K, m, n, out=None):
     with torch.cuda.device(codes.device):
         st = _lib.load().qtip_decode_hyb(out.data_ptr(), codes.data_ptr(), tlut.data_ptr(), K, m, n, _stream())
     _lib.check(st, "qtip_decode_hyb")
+    global launch_count
+    launch_count += 1
     return out
 
 
@@ -144,6 +147,8 @@ def decode_plain(codes, code, K, m, n, tlut=None, out=None):
         st = _lib.load().qtip_decode_plain(out.data_ptr(), codes.data_ptr(), code, None if tl is None else tl.data_ptr(),
                                            K, m, n, _stream())
     _lib.check(st, "qtip_decode_plain")
+    global launch_count
+    launch_count += 1
     return out
 
 
@@ -162,6 +167,8 @@ def decompress_matvec(codes, x, tlut, K, m, n, out=None, workspace=None):
         st = _lib.load().qtip_decompress_matvec(out.data_ptr(), codes.data_ptr(), x.data_ptr(), tlut.data_ptr(), K, m,
                                                 n, bs, workspace.data_ptr(), workspace.numel(), _stream())
     _lib.check(st, "qtip_decompress_matvec")
+    global launch_count
+    launch_count += 1
     return out
 
 
@@ -181,6 +188,8 @@ def decompress_matvec_plain(codes, x, code, K, m, n, out=None, workspace=None):
         st = _lib.load().qtip_decompress_matvec_plain(out.data_ptr(), codes.data_ptr(), x.data_ptr(), code, K, m, n, bs,
                                                       workspace.data_ptr(), workspace.numel(), _stream())
     _lib.check(st, "qtip_decompress_matvec_plain")
+    global launch_count
+    launch_count += 1
     return out
 
 
@@ -213,6 +222,8 @@ def rht(x, sign_in=None, sign_out=None, hadk_bits=None, kfac=1, transpose=False,
                                   None if hadk_bits is None else hadk_bits.data_ptr(), kfac, int(bool(transpose)),
                                   float(scale), _stream())
     _lib.check(st, "qtip_rht")
+    global launch_count
+    launch_count += 1
     return out.reshape(*x.shape[:-1], n)
 
 
@@ -239,6 +250,8 @@ def rht_fused(x, rows, n, out, *, in_row_stride=None, residual=None, residual_ou
                                     F16 if sign_in is None else _dtype_id(sign_in), p(sign_out), n_signs, p(hadk_bits),
                                     kfac, int(bool(transpose)), float(scale), _stream())
     _lib.check(st, "qtip_rht_fused")
+    global launch_count
+    launch_count += 1
     return out
 
 
@@ -246,10 +259,34 @@ def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim
     st = _lib.load().qtip_rope_kv_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
                                          pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), _stream())
     _lib.check(st, "qtip_rope_kv_append")
+    global launch_count
+    launch_count += 1
 
 
 def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
     st = _lib.load().qtip_attn_decode(out.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(),
                                       n_heads, n_kv_heads, head_dim, _stream())
     _lib.check(st, "qtip_attn_decode")
+    global launch_count
+    launch_count += 1
     return out
+
+
+def linear_fused(descs, K, m, n, bs=1):
+    """qtip_linear_fused: one launch for up to four same-shape linears, transforms optionally fused.
+    `descs` is a list of dicts with tensor values for the fields of qtip_linear_desc (missing = NULL):
+    y, codes, tlut, x, workspace, in_raw, residual, residual_out, norm_weight, gate, sign_in, out, sign_out
+    plus floats in_scale, eps, out_scale."""
+    arr = (_lib.LinearDesc * len(descs))()
+    for d, c in zip(descs, arr):
+        for name in ("y", "codes", "tlut", "x", "workspace", "in_raw", "residual", "residual_out", "norm_weight", "gate",
+                     "sign_in", "out", "sign_out"):
+            t = d.get(name)
+            setattr(c, name, None if t is None else t.data_ptr())
+        c.workspace_bytes = d["workspace"].numel()
+        c.in_scale, c.eps, c.out_scale = float(d.get("in_scale", 1.0)), float(d.get("eps", 0.0)), float(d.get("out_scale", 1.0))
+        c.out_dtype = F16 if d.get("out") is None else _dtype_id(d["out"])
+    st = _lib.load().qtip_linear_fused(arr, len(descs), K, m, n, bs, _stream())
+    _lib.check(st, "qtip_linear_fused")
+    global launch_count
+    launch_count += 1

@@ -192,3 +192,49 @@ def test_tensor_parallel_shards_equal_unsharded_layer(tp):
                             scale=1 / math.sqrt(m_r), out_dtype=torch.float16))
     got = torch.cat(outs, dim=1).float()
     assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 1e-3
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+def test_linear_fused_matches_three_kernel_path(K):
+    """qtip_linear_fused (input transform, matvec, output transform in one launch, three linears batched)
+    against the separate RHT / matvec / RHT launches."""
+    import math
+    from qtip_b200 import _lib
+    m = n = 4096
+    lays = [synth.make_layer(m, n, K, seed=700 + 10 * K + i) for i in range(3)]
+    g = torch.Generator().manual_seed(K)
+    raw = torch.randn(n, generator=g).half().to(DEV)
+    res = torch.randn(n, generator=g).half().to(DEV)
+    w = (1 + 0.1 * torch.randn(n, generator=g)).half().to(DEV)
+    need = _lib.load().qtip_matvec_workspace_bytes(m, n, 1)
+    descs, want, res_want = [], [], None
+    res_out = torch.zeros(n, dtype=torch.float16, device=DEV)
+    for i, lay in enumerate(lays):
+        codes, tl = t16(lay["codes"]), torch.from_numpy(lay["tlut"]).to(DEV)
+        SU, SV = torch.from_numpy(lay["SU"]).to(DEV), torch.from_numpy(lay["SV"]).to(DEV) * 32
+        xh = torch.zeros(1, n, dtype=torch.float16, device=DEV)
+        r2 = torch.zeros(n, dtype=torch.float16, device=DEV)
+        ops.rht_fused(raw, 1, n, xh, residual=res, residual_out=r2, norm_weight=w, eps=1e-5, sign_in=SU, transpose=True,
+                      scale=1 / (math.sqrt(n) * 32))
+        y = ops.decompress_matvec(codes, xh, tl, K, m, n)
+        want.append(ops.rht(y, sign_out=SV, scale=1 / math.sqrt(m), out_dtype=torch.float16))
+        res_want = r2
+        descs.append(dict(y=torch.zeros(m, device=DEV), codes=codes, tlut=tl, workspace=torch.zeros(need, dtype=torch.uint8, device=DEV),
+                          in_raw=raw, residual=res, residual_out=res_out if i == 0 else None, norm_weight=w, sign_in=SU,
+                          in_scale=1 / (math.sqrt(n) * 32), eps=1e-5, out=torch.zeros(m, dtype=torch.float16, device=DEV),
+                          sign_out=SV, out_scale=1 / math.sqrt(m)))
+    for _ in range(2):   # twice: the workspace counters must be left ready for the next call
+        for d in descs:
+            d["out"].zero_()
+        ops.linear_fused(descs, K, m, n, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(res_out, res_want)
+        for d, wv in zip(descs, want):
+            assert rel_l2(d["out"].float().cpu().numpy(), wv.float().cpu().numpy()) < 1e-3
+    # no fusion, two linears in one launch == two single launches
+    xs = [torch.from_numpy(l["x"]).to(DEV) for l in lays[:2]]
+    plain = [dict(y=torch.zeros(m, device=DEV), codes=d["codes"], tlut=d["tlut"], workspace=d["workspace"], x=x)
+             for d, x in zip(descs, xs)]
+    ops.linear_fused(plain, K, m, n, 1)
+    for d, x in zip(plain, xs):
+        assert torch.equal(d["y"].view(1, m), ops.decompress_matvec(d["codes"], x, d["tlut"], K, m, n))
