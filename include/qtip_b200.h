@@ -78,6 +78,18 @@ size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
 int qtip_decompress_matvec(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
                            int bs, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Decompress-GEMM for batches up to 64 on the tcgen05 tensor cores (accumulator in tensor memory):
+ * out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T, HYB code, kernel layout.  Replaces
+ * BitshiftLinearKernelAG.forward (lib/codebook/bitshift.py:476-489: decode_compressed to a dense fp16
+ * matrix in HBM, then a dense GEMM) without ever materialising the matrix.
+ * m a multiple of 128, n a multiple of 64; x and codes 16-byte aligned.  status: one zero-initialised
+ * uint32 in device memory; the kernel leaves it 0, or a non-zero code if one of its (bounded) waits on
+ * a shared-memory barrier gave up - the results are then meaningless, but the kernel still terminates
+ * and frees its tensor memory.  When the row ranges leave SMs idle the input columns are split over
+ * two CTAs and `out` is zeroed on the stream first (allocation-free, capturable). */
+int qtip_decompress_gemm(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n, int bs,
+                         unsigned *status, void *stream);
+
 /* One to four QTIP linears of the same shape in ONE launch (e.g. q/k/v, or gate/up), each optionally with
  * its input-side and output-side transforms fused into the matvec kernel, i.e. the whole of
  * BitshiftLinear.forward (lib/codebook/bitshift.py:428-472) for a decode step in one kernel:

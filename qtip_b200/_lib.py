@@ -33,6 +33,7 @@ SIGNATURES = {
     "qtip_matvec_workspace_bytes": (_sz, [_i, _i, _i]),
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_decompress_matvec_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "qtip_decompress_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "qtip_linear_fused": (_i, [ctypes.POINTER(LinearDesc), _i, _i, _i, _i, _i, _vp]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),

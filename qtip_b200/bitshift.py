@@ -107,8 +107,11 @@ class BitshiftLinear(nn.Module):
                 y = ops.decompress_matvec(trellis, xh, self.cb.tlut, self.cb.K, m, n, workspace=self.workspace)
             else:
                 y = ops.decompress_matvec_plain(trellis, xh, self.cb.code, self.cb.K, m, n, workspace=self.workspace)
+        elif self.has_kernel and ops.gemm_supported(m, n, bs):
+            # batches 9..64: decode inside the tensor-core GEMM, the dense matrix never exists
+            y = ops.decompress_gemm(trellis, xh, self.cb.tlut, self.cb.K, m, n)
         else:
-            # larger batches: decode once, dense fp16 GEMM (BitshiftLinearKernelAG upstream, bitshift.py:476-489)
+            # anything else: decode once, dense fp16 GEMM (BitshiftLinearKernelAG upstream, bitshift.py:476-489)
             y = (xh @ self.decode(trellis, m, n).T).float()
 
         # output side: Hadamard (per chunk when column-parallel) -> * SV * 32

@@ -1,0 +1,314 @@
+// Decompress-GEMM for batches 9..64 on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   out (bs, m) fp32 = X (bs, n) fp16 @ decode(codes)^T        HYB code, kernel layout
+//
+// One CTA owns 128 output rows (four 32-row blocks) and a contiguous range of input columns.  The
+// weights are the A operand: D[128 x N] += A[128 x 16] * B[16 x N] with D in tensor memory, A and B
+// in shared memory, K-major, 128-byte swizzle; N = batch rounded up to 16.
+//   * 16 decode warps turn packed codes into fp16 and store them straight into the swizzled A tile
+//     of a ring stage (128 rows x 64 columns = 8 tile blocks, one per warp; two stages are filled
+//     concurrently).  The stores of a warp hit 32 distinct banks.  The same warps copy the 64-column
+//     slice of X into the B tile of the stage.
+//   * one thread issues four tcgen05.mma (K = 16 each) per stage and commits them to the stage's
+//     "empty" barrier; a last commit signals the epilogue.
+//   * warps 0-3 read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 = rows) and
+//     write out (coalesced along rows); with a 2-way column split the two CTAs of a row range add
+//     into a zeroed output (two addends: order-independent, so still deterministic).
+// This replaces decode-to-HBM + dense GEMM of BitshiftLinearKernelAG upstream
+// (lib/codebook/bitshift.py:476-489), which writes and re-reads 16x the packed bytes at 2 bits.
+//
+// Only the decode is expensive (one table lookup + one shared-memory store per state); the MMA work
+// is negligible below batch 256, so the kernel runs at roughly the speed of the batch-1 matvec.
+//
+// Every mbarrier wait is bounded: after kSpinLimit polls the waiter records an error code in
+// `status`, raises a CTA-wide abort flag that makes every later wait fall through, and the kernel
+// still runs to its end, frees its tensor memory and returns (with meaningless results).
+#include "common.cuh"
+
+namespace qtip {
+namespace {
+
+constexpr int kDecodeWarps = 16;
+constexpr int kGemmThreads = (kDecodeWarps + 1) * 32;   // + one control warp (TMEM allocation, MMA issue)
+constexpr int kStages = 4;
+constexpr int kRows = 128;                               // output rows per CTA
+constexpr int kStageCols = 64;                           // input columns per stage (128 bytes of fp16 per row)
+constexpr int kAStageBytes = kRows * kStageCols * 2;     // 16 KiB
+constexpr int kLut512Bytes = 512 * 32 * 4;               // 512 entries x 32 lane-private copies
+constexpr int kMaxN = 64;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+struct GemmCtrl {
+    unsigned long long full[kStages];
+    unsigned long long empty[kStages];
+    unsigned long long done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned *status,
+                                          unsigned code) {
+    if (mbar_try_wait(bar, parity)) return;
+    for (unsigned spin = 0; spin < kSpinLimit; spin++) {
+        if (mbar_try_wait(bar, parity)) return;
+        if (*abort_flag) return;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0u, code);
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int K>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    decompress_gemm_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
+                           const uint32_t *__restrict__ tlut, int m, int n, int bs, int npad, int splitk,
+                           unsigned *__restrict__ status) {
+    constexpr int kBlockBytes = 128 * K;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_addr(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
+    uint8_t *smem = smem_raw + (base - raw);
+    const int b_stage_bytes = npad * 128;
+    // layout: A stages | B stages | LUT | control
+    const uint32_t a_base = base, b_base = base + kStages * kAStageBytes;
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kStages * (kAStageBytes + b_stage_bytes));
+    GemmCtrl *ctl = reinterpret_cast<GemmCtrl *>(smem + kStages * (kAStageBytes + b_stage_bytes) + kLut512Bytes);
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tmem_cols = npad <= 32 ? 32 : 64;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(smem_addr(&ctl->full[s]), 8);     // eight decode warps fill a stage
+            mbar_init(smem_addr(&ctl->empty[s]), 1);    // one tcgen05.commit frees it
+        }
+        mbar_init(smem_addr(&ctl->done), 1);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kDecodeWarps) {
+        // tensor memory for the accumulator: 128 lanes x tmem_cols 32-bit columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&ctl->tmem_base)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // lane-private copies of the 512-entry LUT: entry e, copy l at byte e*128 + l*4
+    for (int i = threadIdx.x; i < 512 * 8; i += kGemmThreads) {
+        const uint32_t e = __ldg(tlut + (i >> 3));
+        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = ctl->tmem_base;
+
+    const int nb = n >> 5;                                  // 32-column blocks per row block
+    const int r0 = blockIdx.x * kRows;                      // first output row of this CTA
+    const int cols_per_split = n / splitk;
+    const int c0 = blockIdx.y * cols_per_split;             // first input column
+    const int nsteps = cols_per_split / kStageCols;
+
+    if (warp < kDecodeWarps) {
+        // ---------------------------------- decode warps ------------------------------------------------
+        const int group = warp >> 3;                        // 0: even stage steps, 1: odd
+        const int w8 = warp & 7, rb = w8 & 3, cb = w8 >> 2; // row block (of 4) and column block (of 2) of the stage
+        const int a = lane >> 2, b = lane & 3;
+        const uint32_t lut_lane = smem_addr(lut) + lane * 4;
+        const uint8_t *src = codes + ((size_t)(r0 / 32 + rb) * nb + (c0 / 32 + cb)) * kBlockBytes + lane * (4 * K);
+        // byte offset inside an A stage of this lane's element (ms, d, ks, c): row 32rb+16ms+8d+a, column 32cb+16ks+8c+2b
+        const uint32_t row_off = (uint32_t)(4 * rb) * 1024u + (uint32_t)a * 128u + (uint32_t)b * 4u;
+        const int tid8 = w8 * 32 + lane;                    // 0..255 within the stage's eight warps
+        // software pipeline: the codes and the x chunk(s) of the NEXT step of this warp are requested before
+        // the current step is decoded, so the global-memory latency is hidden behind a step of work
+        const int chunks = npad * 8;                        // 16-byte chunks of a B tile; <= 2 per thread
+        const bool has0 = tid8 < chunks, has1 = tid8 + 256 < chunks;
+        auto load_x = [&](int step, int ch) -> uint4 {
+            const int brow = ch >> 3, c = ch & 7;
+            if (brow >= bs) return make_uint4(0u, 0u, 0u, 0u);
+            return *reinterpret_cast<const uint4 *>(x + (size_t)brow * n + c0 + step * kStageCols + c * 8);
+        };
+        LaneCodes<K> own_next;
+        uint4 xv0_next = make_uint4(0u, 0u, 0u, 0u), xv1_next = xv0_next;
+        if (group < nsteps) {
+            own_next = load_lane_codes<K>(src + (size_t)group * 2 * kBlockBytes);
+            if (has0) xv0_next = load_x(group, tid8);
+            if (has1) xv1_next = load_x(group, tid8 + 256);
+        }
+        for (int step = group; step < nsteps; step += 2) {
+            const int s = step % kStages, round = step / kStages;
+            const LaneCodes<K> own = own_next;
+            const uint4 xv0 = xv0_next, xv1 = xv1_next;
+            if (step + 2 < nsteps) {
+                own_next = load_lane_codes<K>(src + (size_t)(step + 2) * 2 * kBlockBytes);
+                if (has0) xv0_next = load_x(step + 2, tid8);
+                if (has1) xv1_next = load_x(step + 2, tid8 + 256);
+            }
+            if (round > 0) mbar_wait(smem_addr(&ctl->empty[s]), (round - 1) & 1, abort_flag, status, 1u);
+            LaneCodes<K> nxt;
+#pragma unroll
+            for (int i = 0; i < K; i++) nxt.w[i] = __shfl_sync(kFullMask, own.w[i], lane + 1);
+            // B tile: rows = batch (zero beyond bs), 64 columns of x, 16-byte chunks swizzled by row % 8
+            const uint32_t bst = b_base + s * b_stage_bytes;
+            if (has0) {
+                const int brow = tid8 >> 3, c = tid8 & 7;
+                const uint32_t dst = bst + brow * 128 + ((c ^ (brow & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(xv0.x), "r"(xv0.y), "r"(xv0.z), "r"(xv0.w) : "memory");
+            }
+            if (has1) {
+                const int brow = (tid8 + 256) >> 3, c = tid8 & 7;
+                const uint32_t dst = bst + brow * 128 + ((c ^ (brow & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(xv1.x), "r"(xv1.y), "r"(xv1.z), "r"(xv1.w) : "memory");
+            }
+            const uint32_t ast = a_base + s * kAStageBytes + row_off;
+#pragma unroll
+            for (int tt = 0; tt < 4; tt++) {
+                const int ks = tt >> 1, ms = tt & 1;
+                uint32_t st[4];
+                lane_states<K>(lane_slice<K>(own, tt), lane_slice<K>(nxt, tt), st);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int c = q >> 1, d = q & 1;
+                    const uint32_t h = hyb_hash(st[q]);
+                    uint32_t w;
+                    asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0x7FC0u) << 1)));
+                    w ^= h & 0x8000u;
+                    const uint32_t chunk = (uint32_t)(4 * cb + 2 * ks + c);
+                    const uint32_t dst = ast + (uint32_t)(2 * ms + d) * 1024u + ((chunk ^ (uint32_t)a) << 4);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(w) : "memory");
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_addr(&ctl->full[s]));
+        }
+    } else if (lane == 0) {
+        // ------------------------------------ MMA issue ---------------------------------------------------
+        // instruction descriptor: D fp32, A/B fp16, both K-major, N = npad, M = 128
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+        for (int step = 0; step < nsteps; step++) {
+            const int s = step % kStages, round = step / kStages;
+            mbar_wait(smem_addr(&ctl->full[s]), round & 1, abort_flag, status, 2u);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t adesc = umma_desc(a_base + s * kAStageBytes);
+            const uint64_t bdesc = umma_desc(b_base + s * b_stage_bytes);
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)   // 16 columns = 32 bytes further inside the 128-byte swizzled row
+                umma_f16(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (step | kk) != 0);
+            umma_commit(smem_addr(&ctl->empty[s]));
+        }
+        umma_commit(smem_addr(&ctl->done));
+    }
+
+    if (warp < 4) {
+        // ------------------------------------- epilogue ----------------------------------------------------
+        mbar_wait(smem_addr(&ctl->done), 0u, abort_flag, status, 3u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = r0 + warp * 32 + lane;
+        for (int col = 0; col < npad; col += 8) {
+            uint32_t r[8];
+            const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)col;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                         : "r"(taddr)
+                         : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int bcol = col + j;
+                if (bcol < bs) {
+                    const float v = __uint_as_float(r[j]);
+                    if (splitk == 1) out[(size_t)bcol * m + row] = v;
+                    else atomicAdd(out + (size_t)bcol * m + row, v);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kDecodeWarps) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
+template <int K>
+int launch_gemm(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs, int npad,
+                int splitk, unsigned *status, cudaStream_t s) {
+    const int smem = 1024 + kStages * (kAStageBytes + npad * 128) + kLut512Bytes + 256;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    QTIP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(decompress_gemm_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev] = true;
+    }
+    if (splitk > 1) QTIP_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)bs * m * sizeof(float), s));
+    decompress_gemm_kernel<K><<<dim3(m / kRows, splitk), kGemmThreads, smem, s>>>(out, codes, x, tlut, m, n, bs, npad, splitk,
+                                                                                  status);
+    return check_launch();
+}
+
+}  // namespace
+}  // namespace qtip
+
+using namespace qtip;
+
+extern "C" int qtip_decompress_gemm(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
+                                    int bs, unsigned *status, void *stream) {
+    if (!out || !codes || !x || !tlut || !status || K < 2 || K > 4 || bs < 1 || bs > kMaxN) return QTIP_ERR_BAD_ARG;
+    if (m <= 0 || n <= 0 || (m % kRows) || (n % kStageCols)) return QTIP_ERR_BAD_SHAPE;
+    if ((long)(m >> 5) * (n >> 5) >= (1L << 30)) return QTIP_ERR_BAD_SHAPE;
+    if (!aligned(codes, 16) || !aligned(x, 16) || !aligned(out, 4) || !aligned(tlut, 4) || !aligned(status, 4))
+        return QTIP_ERR_ALIGNMENT;
+    const int npad = (bs + 15) & ~15;
+    // two CTAs per row range while that still leaves SMs idle and the column range divides
+    const int splitk = ((m / kRows) * 2 <= sm_count() && (n % (2 * kStageCols)) == 0) ? 2 : 1;
+    auto *c = static_cast<const uint8_t *>(codes);
+    auto *xh = static_cast<const __half *>(x);
+    auto *t = static_cast<const uint32_t *>(tlut);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 2) return launch_gemm<2>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+    if (K == 3) return launch_gemm<3>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+    return launch_gemm<4>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+}

@@ -15,6 +15,7 @@ from ._lib import CODE_1MAD, CODE_3INST, CODE_HYB, F16, F32  # noqa: F401
 CODE_IDS = {"quantlut_sym": CODE_HYB, "hyb": CODE_HYB, "3inst": CODE_3INST, "1mad": CODE_1MAD}
 HAD_FACTORS = (172, 156, 140, 124, 116, 108, 60, 52, 36, 28, 20, 12)
 MAX_MATVEC_BATCH = 8
+MAX_GEMM_BATCH = 64
 launch_count = 0   # kernel launches issued through this module (bench.py reports it)
 
 
@@ -290,3 +291,37 @@ def linear_fused(descs, K, m, n, bs=1):
     _lib.check(st, "qtip_linear_fused")
     global launch_count
     launch_count += 1
+
+
+_gemm_status = {}
+
+
+def gemm_status(device):
+    """The status word of decompress_gemm on `device` (0 = every launch so far completed its waits)."""
+    t = _gemm_status.get(torch.device(device).index)
+    return 0 if t is None else int(t.item())
+
+
+def decompress_gemm(codes, x, tlut, K, m, n, out=None):
+    """out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T on the tcgen05 tensor cores, 1 <= bs <= 64."""
+    _require_cuda(codes, x, tlut)
+    if x.dtype != torch.float16:
+        x = x.to(torch.float16)
+    x = x.reshape(-1, n).contiguous()
+    bs = x.shape[0]
+    if out is None:
+        out = torch.empty(bs, m, dtype=torch.float32, device=x.device)
+    key = x.device.index
+    if key not in _gemm_status:
+        _gemm_status[key] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().qtip_decompress_gemm(out.data_ptr(), codes.data_ptr(), x.data_ptr(), tlut.data_ptr(), K, m, n, bs,
+                                              _gemm_status[key].data_ptr(), _stream())
+    _lib.check(st, "qtip_decompress_gemm")
+    global launch_count
+    launch_count += 1
+    return out
+
+
+def gemm_supported(m, n, bs):
+    return MAX_MATVEC_BATCH < bs <= MAX_GEMM_BATCH and m % 128 == 0 and n % 64 == 0

@@ -177,3 +177,22 @@ def test_rht_chunked_signs():
                   transpose=True, scale=1 / np.sqrt(seg)).reshape(bs, tp * seg)
     want = O.hadamard((x * su).reshape(bs * tp, seg), hk.numpy(), transpose=True).reshape(bs, tp * seg)
     assert rel_l2(got.cpu().numpy(), want) < 1e-5
+
+
+# ---- tcgen05 decompress-GEMM ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("m,n,bs", [(128, 64, 16), (256, 256, 9), (1024, 2048, 32), (8192, 8192, 16), (4096, 11008, 64),
+                                    (11008, 4096, 33)])
+def test_decompress_gemm(K, m, n, bs):
+    """Tensor-core path against the dense product of the (bit-exact) decoded matrix, fp32 accumulation."""
+    lay = synth.make_layer(m, n, K, seed=3300 + K, bs=bs)
+    codes, x, tl = dev(lay["codes"]), dev(lay["x"]), dev(lay["tlut"])
+    y = ops.decompress_gemm(codes, x, tl, K, m, n)
+    W = ops.decode_hyb(codes, tl, K, m, n)
+    want = x.float() @ W.float().T
+    torch.cuda.synchronize()
+    assert ops.gemm_status(DEV) == 0, "a bounded barrier wait inside the kernel gave up"
+    assert rel_l2(y.cpu().numpy(), want.cpu().numpy()) < 1e-3
+    assert rel_l2(y.cpu().numpy(), want.cpu().numpy()) < 1e-5
+    y2 = ops.decompress_gemm(codes, x, tl, K, m, n)
+    assert torch.equal(y, y2)
