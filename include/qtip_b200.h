@@ -70,7 +70,7 @@ size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
  * decompress_matvec_16_9_{K}_1_{m}_1_{n}(out, compressed, x, codebook)
  * (qtip-kernels/src/qtip_torch.cu:14-57 and :60-671, kernel qtip-kernels/src/inference.cu:168-425)
  * with one shape-generic call, and extends them to bs <= 8 rows of x.
- * out: (bs, m) fp32, OVERWRITTEN (need not be zeroed); x: (bs, n) fp16, 4-byte aligned rows;
+ * out: (bs, m) fp32, OVERWRITTEN (need not be zeroed); x: (bs, n) fp16, 16-byte aligned;
  * codes 16-byte aligned; tlut 512x2 fp16.  m, n multiples of 32.
  * workspace: qtip_matvec_workspace_bytes() bytes, 256-byte aligned, ZEROED ONCE by the caller
  * before its first use (the kernel leaves it zeroed again); calls that may overlap on the device

@@ -5,9 +5,9 @@
 // One CTA owns 128 output rows (four 32-row blocks) and a contiguous range of input columns.  The
 // weights are the A operand: D[128 x N] += A[128 x 16] * B[16 x N] with D in tensor memory, A and B
 // in shared memory, K-major, 128-byte swizzle; N = batch rounded up to 16.
-//   * 16 decode warps turn packed codes into fp16 and store them straight into the swizzled A tile
-//     of a ring stage (128 rows x 64 columns = 8 tile blocks, one per warp; two stages are filled
-//     concurrently).  The stores of a warp hit 32 distinct banks.  The same warps copy the 64-column
+//   * 24 decode warps turn packed codes into fp16 and store them straight into the swizzled A tile
+//     of a ring stage (128 rows x 64 columns = 8 tile blocks, one per warp; three stages are
+//     filled concurrently).  The stores of a warp hit 32 distinct banks.  The same warps copy the 64-column
 //     slice of X into the B tile of the stage.
 //   * one thread issues four tcgen05.mma (K = 16 each) per stage and commits them to the stage's
 //     "empty" barrier; a last commit signals the epilogue.
@@ -28,13 +28,14 @@
 namespace qtip {
 namespace {
 
-constexpr int kDecodeWarps = 16;
+constexpr int kGroups = 3;                               // groups of 8 decode warps; a group fills one stage
+constexpr int kDecodeWarps = 8 * kGroups;
 constexpr int kGemmThreads = (kDecodeWarps + 1) * 32;   // + one control warp (TMEM allocation, MMA issue)
 constexpr int kStages = 4;
 constexpr int kRows = 128;                               // output rows per CTA
 constexpr int kStageCols = 64;                           // input columns per stage (128 bytes of fp16 per row)
 constexpr int kAStageBytes = kRows * kStageCols * 2;     // 16 KiB
-constexpr int kLut512Bytes = 512 * 32 * 4;               // 512 entries x 32 lane-private copies
+constexpr int kLut512Bytes = 1024 * 32 * 4;              // (512 entries + sign-flipped twins) x 32 lane-private copies
 constexpr int kMaxN = 64;
 constexpr unsigned kSpinLimit = 1u << 22;
 
@@ -134,9 +135,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // lane-private copies of the 512-entry LUT: entry e, copy l at byte e*128 + l*4
-    for (int i = threadIdx.x; i < 512 * 8; i += kGemmThreads) {
-        const uint32_t e = __ldg(tlut + (i >> 3));
+    // lane-private copies of the table: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit of
+    // the hash flips the first weight of the pair, so it is folded into the table (no per-state sign op)
+    for (int i = threadIdx.x; i < 1024 * 8; i += kGemmThreads) {
+        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
         reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
     if (warp < kDecodeWarps) {
         // ---------------------------------- decode warps ------------------------------------------------
-        const int group = warp >> 3;                        // 0: even stage steps, 1: odd
+        const int group = warp >> 3;                        // this group fills steps group, group + kGroups, ...
         const int w8 = warp & 7, rb = w8 & 3, cb = w8 >> 2; // row block (of 4) and column block (of 2) of the stage
         const int a = lane >> 2, b = lane & 3;
         const uint32_t lut_lane = smem_addr(lut) + lane * 4;
@@ -176,14 +178,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (has0) xv0_next = load_x(group, tid8);
             if (has1) xv1_next = load_x(group, tid8 + 256);
         }
-        for (int step = group; step < nsteps; step += 2) {
+        for (int step = group; step < nsteps; step += kGroups) {
             const int s = step % kStages, round = step / kStages;
             const LaneCodes<K> own = own_next;
             const uint4 xv0 = xv0_next, xv1 = xv1_next;
-            if (step + 2 < nsteps) {
-                own_next = load_lane_codes<K>(src + (size_t)(step + 2) * 2 * kBlockBytes);
-                if (has0) xv0_next = load_x(step + 2, tid8);
-                if (has1) xv1_next = load_x(step + 2, tid8 + 256);
+            if (step + kGroups < nsteps) {
+                own_next = load_lane_codes<K>(src + (size_t)(step + kGroups) * 2 * kBlockBytes);
+                if (has0) xv0_next = load_x(step + kGroups, tid8);
+                if (has1) xv1_next = load_x(step + kGroups, tid8 + 256);
             }
             if (round > 0) mbar_wait(smem_addr(&ctl->empty[s]), (round - 1) & 1, abort_flag, status, 1u);
             LaneCodes<K> nxt;
@@ -212,8 +214,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const int c = q >> 1, d = q & 1;
                     const uint32_t h = hyb_hash(st[q]);
                     uint32_t w;
-                    asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0x7FC0u) << 1)));
-                    w ^= h & 0x8000u;
+                    asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0xFFC0u) << 1)));
                     const uint32_t chunk = (uint32_t)(4 * cb + 2 * ks + c);
                     const uint32_t dst = ast + (uint32_t)(2 * ms + d) * 1024u + ((chunk ^ (uint32_t)a) << 4);
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(w) : "memory");

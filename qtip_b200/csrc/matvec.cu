@@ -349,13 +349,22 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (threadIdx.x == 0) sh->is_last = 0;
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
-    // flips the sign of the first (low) half of the pair
-    for (int i = threadIdx.x; i < 1024 * 8; i += kThreads) {
-        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
-        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
-    }
+    // flips the sign of the first (low) half of the pair.  The 8 table words of this thread are requested
+    // now (weights), stored after the activation loads below have been issued as well, so that the two
+    // global round trips overlap.
+    uint32_t lut_e[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) lut_e[k] = __ldg(tlut + (((threadIdx.x + k * kThreads) >> 3) & 511));
     grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
+    auto store_lut = [&]() {
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int i = threadIdx.x + k * kThreads;
+            const uint32_t e = lut_e[k] ^ ((uint32_t)(i >> 12) << 15);
+            reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+        }
+    };
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
         if (P.in.x_raw) {
@@ -365,14 +374,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             const FusedIn &I = P.in;
             const int nvec = n >> 3;
             float ss = 0.f;
+            bool lut_stored = false;
             for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
                 const size_t j = (size_t)vi * 8;
-                float v[8], rs[8], w[8], gt[8], sg[8];
+                float v[8], rs[8], gt[8], sg[8];
                 load8_f16(I.x_raw, j, v);
                 if (I.residual) load8_f16(I.residual, j, rs);
-                if (I.norm_weight) load8_f16(I.norm_weight, j, w);
-                if (I.gate) load8_f16(I.gate, j, gt);
-                if (I.sign_in) load8_f16(I.sign_in, j, sg);
+                if (I.gate && !I.norm_weight) load8_f16(I.gate, j, gt);
+                if (I.sign_in && !I.norm_weight) load8_f16(I.sign_in, j, sg);
+                if (!lut_stored) { store_lut(); lut_stored = true; }   // table stores while the loads above are in flight
                 if (I.residual) {
 #pragma unroll
                     for (int k = 0; k < 8; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));   // fp16 residual stream
@@ -390,6 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     fscratch[pad((int)j + k)] = v[k];
                 }
             }
+            if (!lut_stored) store_lut();
             if (I.norm_weight) {
                 const float r = rsqrtf(block_sum(ss, sh->warp_sums) / (float)n + I.eps);
                 for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {   // each thread revisits its own values
@@ -418,13 +429,24 @@ __global__ void __launch_bounds__(kThreads, 1)
                 reinterpret_cast<__half2 *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = h;
             }
         } else {
-            const uint32_t *xw = reinterpret_cast<const uint32_t *>(x);
-            const int words = bs * (n >> 1);
-            for (int i = threadIdx.x; i < words; i += kThreads) {
-                const int blk = i >> 4, w = i & 15;          // 16 words per 32-column block
-                reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = __ldg(xw + i);
+            // 4 words (8 values) per thread and trip, requested before the table stores
+            const uint4 *xw = reinterpret_cast<const uint4 *>(x);
+            const int quads = bs * (n >> 3);
+            bool lut_stored = false;
+            for (int i = threadIdx.x; i < quads; i += kThreads) {
+                const uint4 q = __ldg(xw + i);
+                if (!lut_stored) { store_lut(); lut_stored = true; }
+                const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int wi = i * 4 + k, blk = wi >> 4, w = wi & 15;   // 16 words per 32-column block
+                    reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = wv[k];
+                }
             }
+            if (!lut_stored) store_lut();
         }
+    } else {
+        store_lut();
     }
     __syncthreads();
 
@@ -502,6 +524,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             int p = 0;
             while ((1 << p) < m) p++;
             const int mvec = m >> 3;
+            // sign_out of this thread's first vector, requested together with the first y loads
+            float sg0[8];
+            if (P.ep.sign_out && threadIdx.x < mvec) load8_f32(P.ep.sign_out, (size_t)threadIdx.x * 8, sg0);
             for (int b = 0; b < bs; b++) {
                 for (int vi = threadIdx.x; vi < mvec; vi += kThreads) {
                     const float4 *src = reinterpret_cast<const float4 *>(out + (size_t)b * m + (size_t)vi * 8);
@@ -515,11 +540,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int vi = threadIdx.x; vi < mvec; vi += kThreads) {
                     const size_t j = (size_t)vi * 8;
                     float y[8], sg[8];
-                    if (P.ep.sign_out) load8_f32(P.ep.sign_out, j, sg);
+                    if (P.ep.sign_out && vi != (int)threadIdx.x) load8_f32(P.ep.sign_out, j, sg);
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         y[k] = f[pad((int)j + k)] * P.ep.scale;
-                        if (P.ep.sign_out) y[k] *= sg[k];
+                        if (P.ep.sign_out) y[k] *= (vi == (int)threadIdx.x) ? sg0[k] : sg[k];
                     }
                     if (P.ep.dtype == QTIP_F16) store8_f16(static_cast<__half *>(P.ep.final), (size_t)b * m + j, y);
                     else store8_f32(static_cast<float *>(P.ep.final), (size_t)b * m + j, y);
@@ -618,7 +643,7 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
     if (m <= 0 || n <= 0 || (m & 31) || (n & 31) || (size_t)(m >> 5) * 4 > kCounterBytes) return QTIP_ERR_BAD_SHAPE;
     if ((long)(m >> 5) * (n >> 5) >= (1L << 30)) return QTIP_ERR_BAD_SHAPE;  // block indices are 32-bit
     if (!workspace || workspace_bytes < qtip_matvec_workspace_bytes(m, n, bs)) return QTIP_ERR_WORKSPACE;
-    if (!aligned(workspace, 256) || !aligned(codes, 16) || !aligned(x, 4) || !aligned(out, 4)) return QTIP_ERR_ALIGNMENT;
+    if (!aligned(workspace, 256) || !aligned(codes, 16) || !aligned(x, 16) || !aligned(out, 4)) return QTIP_ERR_ALIGNMENT;
     return QTIP_OK;
 }
 

@@ -238,3 +238,41 @@ def test_linear_fused_matches_three_kernel_path(K):
     ops.linear_fused(plain, K, m, n, 1)
     for d, x in zip(plain, xs):
         assert torch.equal(d["y"].view(1, m), ops.decompress_matvec(d["codes"], x, d["tlut"], K, m, n))
+
+
+def test_quip_lib_op_under_graph_capture():
+    """The torch op boundary (lib/codebook/__init__.py:68-93 upstream): eager call and CUDA-graph replay."""
+    from qtip_b200 import codebook_ops
+    m, n, K = 4096, 4096, 3
+    lay = synth.make_layer(m, n, K, seed=21)
+    op = codebook_ops.register(m, n, K)
+    trellis, tl = t16(lay["codes"]), torch.from_numpy(lay["tlut"]).to(DEV)
+    x = torch.from_numpy(lay["x"]).to(DEV).float()
+    y = op(trellis, x, tl)
+    want = C.matvec_kernel(lay["codes"], m, n, K, lay["tlut"], lay["x"])
+    assert y.shape == (1, m) and rel_l2(y.cpu().numpy(), want) < 2e-6
+    ops.matvec_workspace(m, n, 1, DEV)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        op(trellis, x, tl)
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            y2 = op(trellis, x, tl)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
+
+
+def test_cache_hatw_dense_path_matches_fused_path():
+    """train-fixW (dense manifest, lib/codebook/bitshift.py:389-413 upstream) against the fused eval path."""
+    m, n, K = 1376, 512, 2
+    lay = synth.make_layer(m, n, K, seed=33, bs=3)
+    q = QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, "quantlut_sym").to(DEV)
+    qd = QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, "quantlut_sym", mode="train-fixW").to(DEV)
+    for mod in (q, qd):
+        mod.trellis.copy_(t16(lay["codes"])); mod.tlut.copy_(torch.from_numpy(lay["tlut"]))
+        mod.SU.copy_(torch.from_numpy(lay["SU"])); mod.SV.copy_(torch.from_numpy(lay["SV"]))
+    x = torch.from_numpy(lay["x"]).to(DEV)
+    assert rel_l2(qd(x).float().cpu().numpy(), q(x).float().cpu().numpy()) < 3e-3

@@ -57,3 +57,34 @@ def test_quantized_linear_state_dict_keys():
     assert q.K_left == 172 and q.K_right == 1 and q.has_kernel
     q3 = QuantizedLinear(256, 256, 16, 16, 16, 2, 1, 0, '3inst')
     assert q3.tlut is None and not q3.has_kernel
+
+
+def test_unpack_quip_scale_folding():
+    """lib/utils/data_utils.py:281-307 upstream: where the weight scale goes for rcp 0 / 1 / 2."""
+    from qtip_b200.checkpoint import unpack_quip
+    m, n, K = 64, 128, 2
+    g = torch.Generator().manual_seed(0)
+    base = dict(trellis=torch.randint(-2**15, 2**15, (m * n // 256, 16 * K), generator=g).to(torch.int16),
+                SU=torch.randn(n, generator=g).sign().half(), SV=torch.randn(m, generator=g).sign().half(),
+                tlut=torch.randn(512, 2, generator=g).half())
+    q = unpack_quip(QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, 'quantlut_sym'), dict(base, Wscale=torch.tensor(0.5)))
+    assert torch.equal(q.SV, base["SV"].float() * 0.5) and torch.equal(q.SU, base["SU"]) and int(q.rcp) == 0
+    assert torch.equal(q.trellis, base["trellis"]) and torch.equal(q.tlut.data, base["tlut"])
+    ws = torch.arange(1, 9).float()
+    q = unpack_quip(QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, 'quantlut_sym'), dict(base, Wscale=ws, rcp=1, tp_rank=8))
+    assert int(q.rcp) == 1 and int(q.tp_rank) == 8 and torch.equal(q.SV, base["SV"].float())
+    assert torch.equal(q.SU.float(), (base["SU"].float().reshape(8, -1) * ws[:, None]).reshape(-1))
+    q = unpack_quip(QuantizedLinear(n, m, 16, 16, 16, K, 2, 9, 'quantlut_sym'), dict(base, Wscale=ws, rcp=2, tp_rank=8))
+    assert int(q.rcp) == 2 and torch.equal(q.SU, base["SU"])
+    assert torch.equal(q.SV, (base["SV"].float().reshape(8, -1) * ws[:, None]).reshape(-1))
+
+
+def test_torch_ops_register_with_fake_impl():
+    from qtip_b200 import codebook_ops
+    assert len(codebook_ops.UPSTREAM_TABLE) == 61
+    op = codebook_ops.register(4096, 11008, 2)
+    assert op is codebook_ops.register(4096, 11008, 2)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        y = op(torch.empty(4096 * 11008 // 256, 32, dtype=torch.int16), torch.empty(1, 11008), torch.empty(512, 2, dtype=torch.float16))
+        assert y.shape == (1, 4096) and y.dtype == torch.float32
