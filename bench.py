@@ -186,7 +186,8 @@ def measure_matvec_roofline(model, torch, reps=5):
 def run_gpu(args):
     import torch
     import torch.distributed as dist
-    from qtip_b200.llama import LLAMA2_7B, QtipLlama
+    from qtip_b200.llama import LLAMA2_7B, LLAMA3_405B, QtipLlama
+    shape = LLAMA3_405B if args.workload == "llama3-405b" else LLAMA2_7B
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -200,11 +201,11 @@ def run_gpu(args):
     torch.cuda.manual_seed(1234)  # same sampler draws on every rank
     # N > 1: the one sequence is decoded tensor-parallel over the N GPUs (column/row-parallel shards, per-GPU
     # Hadamard transforms, one NCCL all-reduce after o_proj and after down_proj)
-    model = QtipLlama(LLAMA2_7B, max_positions=args.prompt + 2 * (warmup + steps) + 8, device=dev, seed=3000,
+    model = QtipLlama(shape, max_positions=args.prompt + 2 * (warmup + steps) + 8, device=dev, seed=3000,
                       tp_rank=rank, tp_size=world, group=dist.group.WORLD if world > 1 else None)
     model.capture()
     g = torch.Generator().manual_seed(3)
-    prompt = torch.randint(0, LLAMA2_7B.vocab, (args.prompt,), generator=g)
+    prompt = torch.randint(0, shape.vocab, (args.prompt,), generator=g)
 
     def barrier():
         if world > 1:
@@ -259,25 +260,38 @@ def run_gpu(args):
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = byts / us / 1e3  # GB/s
         traffic = [NCU_TRAFFIC_BYTES.get(s) for s in llama7b_linears()]
-        traffic = None if world > 1 or any(t is None for t in traffic) else sum(traffic) / len(traffic)
-        sec, threads = cpu_layer_seconds(repeats=3)
-        cpu_tok_s = 1.0 / (32 * sec)
+        seven_b = args.workload == "llama2-7b"
+        traffic = None if world > 1 or not seven_b or any(t is None for t in traffic) else sum(traffic) / len(traffic)
+        if seven_b:
+            sec, threads = cpu_layer_seconds(repeats=3)
+            cpu_tok_s = 1.0 / (32 * sec)
+        else:
+            sec, threads = cpu_layer_seconds(repeats=1)
+            # the C port is timed on the 7B-shaped layer and scaled by weights per layer and by layers
+            w7 = sum(m * n for (m, n) in llama7b_linears())
+            wl = (2 * shape.hidden ** 2 + 2 * shape.hidden * shape.n_kv_heads * shape.head_dim + 3 * shape.hidden * shape.mlp)
+            cpu_tok_s = 1.0 / (sec * wl / w7 * shape.n_layers)
         out = {
-            "metric": METRIC, "value": steps / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "metric": METRIC if args.workload == "llama2-7b" else METRIC.replace("Llama-2-7B", "Llama-3.1-405B"),
+            "value": steps / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak",
-            "vs_baseline": steps / (ms / 1e3) / PUBLISHED_TOK_S, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "Llama-2-7B shape (32 layers, hidden 4096, 32 heads, MLP 11008, vocab 32000), every linear "
-                                   "2-bit HYB QTIP (L=16, Q=9, V=2, 16x16 tiles), batch 1, 128-token prompt, CUDA-graph decode",
-                       "l2": "each step streams 1.6 GB of packed codes and a 262 MB lm_head, far larger than L2",
+            "vs_baseline": steps / (ms / 1e3) / PUBLISHED_TOK_S if args.workload == "llama2-7b" else None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": (f"{'Llama-3.1-405B' if args.workload == 'llama3-405b' else 'Llama-2-7B'} shape "
+                                    f"({shape.n_layers} layers, hidden {shape.hidden}, {shape.n_heads} heads, MLP {shape.mlp}, "
+                                    f"vocab {shape.vocab}), every linear 2-bit HYB QTIP (L=16, Q=9, V=2, 16x16 tiles), "
+                                    f"batch 1, {args.prompt}-token prompt, CUDA-graph decode"),
+                       "l2": "each step streams all packed codes (1.6 GB for the 7B shape) and the lm_head, far larger than L2",
                        "parallelism": f"tp{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "kernel": "matvec_hyb_kernel<2>", "us_per_launch": us,
                          "algorithmic_bytes_per_launch": byts, "peak_source": "MEASURED_PEAKS.json hbm_gbs"
                          if "hbm_gbs" in peaks else "fallback 6650 GB/s"},
             "cpu_baseline": {"value": cpu_tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
-                             "sample": "the seven QTIP linears of one decoder layer through the C restatement "
-                                       "(median of 3), scaled by 32 layers; attention, norms, lm_head not included"},
+                             "sample": "the seven QTIP linears of one Llama-2-7B-shaped decoder layer through the C "
+                                       "restatement, scaled to the workload's weights per token; attention, norms, "
+                                       "lm_head not included"},
             "e2e": {"value": steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": 8},
             "gpu_launches": model.n_launches_per_step * steps,
@@ -298,6 +312,8 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=PROMPT_TOKENS, help="prompt length (128 in the benchmark configuration)")
+    ap.add_argument("--workload", default="llama2-7b", choices=["llama2-7b", "llama3-405b"],
+                    help="llama3-405b: the 126-layer shape of the tensor-parallel configuration (256-token prompt)")
     ap.add_argument("--impl", default="qtip_b200", choices=["qtip_b200", "reference"])
     args = ap.parse_args()
     if args.impl == "reference":

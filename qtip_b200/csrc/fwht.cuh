@@ -90,7 +90,7 @@ __device__ __forceinline__ void store8_f32(float *p, size_t i, const float (&o)[
 
 // SwiGLU product as fp16 tensors would compute it: silu(gate) rounded to fp16, product rounded to fp16.
 __device__ __forceinline__ float swiglu_fp16(float gate, float up) {
-    const __half sg = __float2half_rn(gate / (1.0f + __expf(-gate)));
+    const __half sg = __float2half_rn(__fdividef(gate, 1.0f + __expf(-gate)));
     return __half2float(__hmul(sg, __float2half_rn(up)));
 }
 

@@ -349,22 +349,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (threadIdx.x == 0) sh->is_last = 0;
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
-    // flips the sign of the first (low) half of the pair.  The 8 table words of this thread are requested
-    // now (weights), stored after the activation loads below have been issued as well, so that the two
-    // global round trips overlap.
-    uint32_t lut_e[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) lut_e[k] = __ldg(tlut + (((threadIdx.x + k * kThreads) >> 3) & 511));
+    // flips the sign of the first (low) half of the pair
+    for (int i = threadIdx.x; i < 1024 * 8; i += kThreads) {
+        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
+        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+    }
     grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
-    auto store_lut = [&]() {
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int i = threadIdx.x + k * kThreads;
-            const uint32_t e = lut_e[k] ^ ((uint32_t)(i >> 12) << 15);
-            reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
-        }
-    };
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
         if (P.in.x_raw) {
@@ -374,7 +365,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             const FusedIn &I = P.in;
             const int nvec = n >> 3;
             float ss = 0.f;
-            bool lut_stored = false;
             for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
                 const size_t j = (size_t)vi * 8;
                 float v[8], rs[8], gt[8], sg[8];
@@ -382,7 +372,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (I.residual) load8_f16(I.residual, j, rs);
                 if (I.gate && !I.norm_weight) load8_f16(I.gate, j, gt);
                 if (I.sign_in && !I.norm_weight) load8_f16(I.sign_in, j, sg);
-                if (!lut_stored) { store_lut(); lut_stored = true; }   // table stores while the loads above are in flight
                 if (I.residual) {
 #pragma unroll
                     for (int k = 0; k < 8; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));   // fp16 residual stream
@@ -400,7 +389,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     fscratch[pad((int)j + k)] = v[k];
                 }
             }
-            if (!lut_stored) store_lut();
             if (I.norm_weight) {
                 const float r = rsqrtf(block_sum(ss, sh->warp_sums) / (float)n + I.eps);
                 for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {   // each thread revisits its own values
@@ -429,13 +417,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 reinterpret_cast<__half2 *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = h;
             }
         } else {
-            // 4 words (8 values) per thread and trip, requested before the table stores
+            // 4 words (8 values) per thread and trip
             const uint4 *xw = reinterpret_cast<const uint4 *>(x);
             const int quads = bs * (n >> 3);
-            bool lut_stored = false;
             for (int i = threadIdx.x; i < quads; i += kThreads) {
                 const uint4 q = __ldg(xw + i);
-                if (!lut_stored) { store_lut(); lut_stored = true; }
                 const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
@@ -443,10 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     reinterpret_cast<uint32_t *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = wv[k];
                 }
             }
-            if (!lut_stored) store_lut();
         }
-    } else {
-        store_lut();
     }
     __syncthreads();
 

@@ -25,7 +25,6 @@ namespace qtip {
 namespace {
 
 constexpr int kRhtThreads = 1024;
-constexpr int kRowsPerCta = 16;  // hadK output rows per CTA
 
 struct RhtArgs {
     void *out; const void *in; const void *sign_in; const float *sign_out; const uint32_t *hadk_bits;
@@ -33,6 +32,7 @@ struct RhtArgs {
     long in_row_stride;  // elements between input rows (0 = every row reads the same input)
     int out_dtype, in_dtype, sign_in_dtype;
     int n, p, sign_rep, kfac, transpose;
+    int rpc;             // hadK output rows per CTA (4, 8 or 16)
     int vec_ok;          // every buffer is 16-byte aligned and n, strides are multiples of 8: 8-wide loads / stores
     float scale, eps;
 };
@@ -55,24 +55,25 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     extern __shared__ __align__(16) float sm[];
     const int n = a.n, kfac = a.kfac;
     float *v = sm;                            // n values, padded (see pad())
-    float *hs = sm + pad(n) + 1;              // kfac x kRowsPerCta signs (+-1.0f), [k][row], only when kfac > 1
+    const int rpc = a.rpc;
+    float *hs = sm + pad(n) + 1;              // kfac x rpc signs (+-1.0f), [k][row], only when kfac > 1
     hs = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(hs) + 15) & ~(uintptr_t)15);
-    float *scratch = hs + (kfac > 1 ? kRowsPerCta * kfac : 0);  // 32 floats (block_sum)
+    float *scratch = hs + (kfac > 1 ? rpc * kfac : 0);            // 32 floats (block_sum)
     uint32_t *bits = reinterpret_cast<uint32_t *>(scratch + 32);  // the packed hadK matrix, kfac * ceil(kfac/32) words
     const long row = blockIdx.y;
     const size_t sign_off = (size_t)(row % a.sign_rep) * n;
     const size_t in_off = (size_t)row * a.in_row_stride, out_off = (size_t)row * n;
 
-    const int i0 = blockIdx.x * kRowsPerCta;
-    const int rows_here = min(kRowsPerCta, kfac - i0);
+    const int i0 = blockIdx.x * rpc;
+    const int rows_here = min(rpc, kfac - i0);
     if (kfac > 1) {
         // one coalesced read of the bit matrix, then hs[k][il] = hadK[i0+il][k]
         // (hadK[k][i0+il] for the transposed, input-side transform)
         const int wpr = (kfac + 31) >> 5;
         for (int i = threadIdx.x; i < kfac * wpr; i += blockDim.x) bits[i] = a.hadk_bits[i];
         __syncthreads();
-        for (int idx = threadIdx.x; idx < kRowsPerCta * kfac; idx += blockDim.x) {
-            const int k = idx >> 4, il = idx & (kRowsPerCta - 1);
+        for (int idx = threadIdx.x; idx < rpc * kfac; idx += blockDim.x) {
+            const int k = idx / rpc, il = idx - k * rpc;
             float sgn = 0.f;
             if (il < rows_here) {
                 const int rr = a.transpose ? k : (i0 + il), cc = a.transpose ? (i0 + il) : k;
@@ -151,11 +152,10 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     __syncthreads();
 
     const int p = a.p;
-    fwht_shared(v, n, p);
-
     const int len = 1 << p;
     const float scale = a.scale;
     if (kfac == 1) {
+        fwht_shared(v, n, p);
         if (vec) {
             for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
                 float y[8], sg[8];
@@ -177,34 +177,63 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
         }
         return;
     }
-    // hadK multiply: output (i0 + il, j) = sum_k hs[k][il] * v[k*len + j].  A thread owns 4 rows of one
-    // column: per k one value and one 16-byte broadcast load of 4 signs feed 4 multiply-adds.
-    const int items = (kRowsPerCta / 4) * len;
-    for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
-        const int j = idx & (len - 1), il = (idx >> p) * 4;
-        // sign_out of the 4 outputs, requested before the long loop
-        float so[4] = {1.f, 1.f, 1.f, 1.f};
-        if (a.sign_out) {
+    // n = kfac * 2^p.  The two factors of the transform commute, so the +-1 multiply runs FIRST, on the
+    // untransformed values, and only this CTA's rpc output rows go through the Walsh-Hadamard passes:
+    //   w[il][j] = sum_k hs[k][il] * v[k*len + j]   then   FWHT over j of each row.
+    // A thread owns 4 rows of one column: per k one value and one 16-byte broadcast load of 4 signs.
+    // The products stay in registers until every thread has finished reading v; the rows are then written over
+    // the start of v (the host guarantees at most 4 items per thread).
+    const int items = (rpc >> 2) * len;
+    float acc[4][4];
 #pragma unroll
-            for (int r = 0; r < 4; r++)
-                if (il + r < rows_here) so[r] = a.sign_out[sign_off + (size_t)(i0 + il + r) * len + j];
-        }
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t = 0; t < 4; t++) {
+        const int idx = threadIdx.x + t * blockDim.x;
+#pragma unroll
+        for (int r = 0; r < 4; r++) acc[t][r] = 0.f;
+        if (idx < items) {
+            const int j = idx & (len - 1), il = (idx >> p) * 4;
 #pragma unroll 4
-        for (int k = 0; k < kfac; k++) {
-            const float x = v[pad(k * len + j)];
-            const float4 h = *reinterpret_cast<const float4 *>(hs + k * kRowsPerCta + il);
-            acc[0] = fmaf(h.x, x, acc[0]); acc[1] = fmaf(h.y, x, acc[1]);
-            acc[2] = fmaf(h.z, x, acc[2]); acc[3] = fmaf(h.w, x, acc[3]);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            if (il + r < rows_here) {
-                const size_t o = (size_t)(i0 + il + r) * len + j;
-                const float y = acc[r] * scale * so[r];
-                if (a.out_dtype == QTIP_F16) static_cast<__half *>(a.out)[out_off + o] = __float2half_rn(y);
-                else static_cast<float *>(a.out)[out_off + o] = y;
+            for (int k = 0; k < kfac; k++) {
+                const float x = v[pad(k * len + j)];
+                const float4 h = *reinterpret_cast<const float4 *>(hs + k * rpc + il);
+                acc[t][0] = fmaf(h.x, x, acc[t][0]); acc[t][1] = fmaf(h.y, x, acc[t][1]);
+                acc[t][2] = fmaf(h.z, x, acc[t][2]); acc[t][3] = fmaf(h.w, x, acc[t][3]);
             }
+        }
+    }
+    __syncthreads();
+    float *wbuf = v;
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int idx = threadIdx.x + t * blockDim.x;
+        if (idx < items) {
+            const int j = idx & (len - 1), il = (idx >> p) * 4;
+#pragma unroll
+            for (int r = 0; r < 4; r++) wbuf[pad((il + r) * len + j)] = acc[t][r];
+        }
+    }
+    __syncthreads();
+    fwht_shared(wbuf, rpc * len, p);
+    const int total = rows_here * len;
+    if (vec && (len & 7) == 0) {
+        for (int e = threadIdx.x * 8; e < total; e += blockDim.x * 8) {
+            const size_t o = (size_t)i0 * len + e;      // rows of this CTA are contiguous in the output
+            float y[8], sg[8];
+            if (a.sign_out) load8_f32(a.sign_out, sign_off + o, sg);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                y[k] = wbuf[pad(e + k)] * scale;
+                if (a.sign_out) y[k] *= sg[k];
+            }
+            store8(a.out, a.out_dtype, out_off + o, y);
+        }
+    } else {
+        for (int e = threadIdx.x; e < total; e += blockDim.x) {
+            const size_t o = (size_t)i0 * len + e;
+            float y = wbuf[pad(e)] * scale;
+            if (a.sign_out) y *= a.sign_out[sign_off + o];
+            if (a.out_dtype == QTIP_F16) static_cast<__half *>(a.out)[out_off + o] = __float2half_rn(y);
+            else static_cast<float *>(a.out)[out_off + o] = y;
         }
     }
 }
@@ -221,8 +250,15 @@ int launch_rht(RhtArgs a, long rows, void *stream) {
     int p = 0;
     while ((1 << p) < len) p++;
     a.p = p;
-    const size_t smem = ((size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)kRowsPerCta * a.kfac : 0) + 32 +
-                         (a.kfac > 1 ? (size_t)a.kfac * ((a.kfac + 31) / 32) : 0)) * sizeof(float);
+    // rows of the factor matrix per CTA: 8, or 4 when a row is long - a thread keeps at most 4 x 4 products
+    // in registers, so (rpc / 4) * len <= 4 * kRhtThreads
+    auto smem_for = [&](int rpc) {
+        return ((size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)rpc * a.kfac : 0) + 32 +
+                (a.kfac > 1 ? (size_t)a.kfac * ((a.kfac + 31) / 32) : 0)) * sizeof(float);
+    };
+    a.rpc = len >= 1024 ? 4 : 8;
+    if (a.kfac > 1 && (a.rpc / 4) * len > 4 * kRhtThreads) return QTIP_ERR_BAD_SHAPE;
+    const size_t smem = smem_for(a.rpc);
     {
         const void *ptrs[] = {a.out, a.in, a.residual, a.residual_out, a.gate, a.sign_in, a.sign_out, a.norm_weight};
         bool ok = (a.n % 8 == 0) && (a.in_row_stride % 8 == 0);
@@ -238,7 +274,7 @@ int launch_rht(RhtArgs a, long rows, void *stream) {
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.kfac > 1 ? (a.kfac + kRowsPerCta - 1) / kRowsPerCta : 1, (unsigned)rows);
+    cfg.gridDim = dim3(a.kfac > 1 ? (a.kfac + a.rpc - 1) / a.rpc : 1, (unsigned)rows);
     cfg.blockDim = dim3(kRhtThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);

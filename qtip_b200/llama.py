@@ -36,6 +36,8 @@ class LlamaShape:
 
 
 LLAMA2_7B = LlamaShape()
+LLAMA3_405B = LlamaShape(n_layers=126, hidden=16384, n_heads=128, n_kv_heads=8, head_dim=128, mlp=53248, vocab=128256,
+                         rms_eps=1e-5, rope_theta=500000.0, K=2)
 
 
 class _Linear:
@@ -132,8 +134,10 @@ class QtipLlama:
         self.workspaces = [self.workspace] + [torch.zeros(need, dtype=torch.uint8, device=dev) for _ in range(2)]
         pow2 = lambda d: d & (d - 1) == 0  # noqa: E731
         # which transforms can ride inside the matvec launch (powers of two only; see qtip_linear_fused)
-        self.fuse_in_h, self.fuse_in_hl, self.fuse_in_m = pow2(s.hidden), pow2(H), pow2(MLP)
-        self.fuse_out_h, self.fuse_out_hl, self.fuse_out_kv, self.fuse_out_m = pow2(s.hidden), pow2(H), pow2(KV), pow2(MLP)
+        fin = lambda d: pow2(d) and d <= 8192   # the in-kernel input transform needs its fp32 scratch in shared memory  # noqa: E731
+        self.fuse_in_h, self.fuse_in_hl, self.fuse_in_m = fin(s.hidden), fin(H), fin(MLP)
+        fout = lambda d: pow2(d) and d <= 16384  # noqa: E731
+        self.fuse_out_h, self.fuse_out_hl, self.fuse_out_kv, self.fuse_out_m = fout(s.hidden), fout(H), fout(KV), fout(MLP)
         self.graph = None
         self.n_launches_per_step = None   # counted while the step runs (library launches only)
 

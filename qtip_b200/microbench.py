@@ -70,8 +70,49 @@ def plain_launches(m, n, K, bs, code, count, device="cuda:0"):
     torch.cuda.synchronize(device)
 
 
+def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0):
+    """Input-side transform (fp16 in, SwiGLU gate, signs, fp16 out) of `rows` rows of width n."""
+    import math
+    k = ops.had_factor(n)
+    bits = None if k == 1 else ops.pack_hadk(ops.get_hadK(n)[0].to(device))
+    x = torch.randn(rows, n, device=device).half()
+    gate = torch.randn(rows, n, device=device).half()
+    su = torch.ones(n, device=device, dtype=torch.float16)
+    out = torch.empty(rows, n, device=device, dtype=torch.float16)
+
+    def launch():
+        ops.rht_fused(x, rows, n, out, gate=gate, sign_in=su, hadk_bits=bits, kfac=k, transpose=True, scale=1 / math.sqrt(n))
+
+    if plain:
+        for _ in range(plain):
+            launch()
+        torch.cuda.synchronize(device)
+        return None
+    stream = torch.cuda.Stream(device=device)
+    stream.wait_stream(torch.cuda.current_stream(device))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        launch()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(launches):
+                launch()
+    torch.cuda.current_stream(device).wait_stream(stream)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) * 1e3 / (replays * launches)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--rht", default="", help="comma-separated widths: time the transform kernel instead of the matvec")
     ap.add_argument("--shapes", default=LLAMA7B)
     ap.add_argument("--bits", default="2,3,4")
     ap.add_argument("--batch", default="1")
@@ -86,6 +127,12 @@ def main():
                                            "MEASURED_PEAKS.json")))["hbm_gbs"]
     except (OSError, KeyError):
         pass
+    if args.rht:
+        for n in (int(v) for v in args.rht.split(",")):
+            us = time_rht(n, plain=args.plain_launches)
+            if us is not None:
+                print(f"rht n={n} (factor {ops.had_factor(n)}): {us:7.2f} us per launch (back-to-back launches in one graph)", flush=True)
+        return
     rows = []
     for K in (int(b) for b in args.bits.split(",")):
         for shape in args.shapes.split(","):
