@@ -52,19 +52,6 @@ __device__ __forceinline__ void fwht_shared(float *v, int n, int p) {
     }
 }
 
-// Sum over the CTA (scratch: one float per warp).  Contains two barriers.
-__device__ __forceinline__ float block_sum(float x, float *scratch) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(kFullMask, x, o);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();
-    if (lane == 0) scratch[warp] = x;
-    __syncthreads();
-    float t = 0.f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += scratch[w];
-    return t;
-}
-
 // 8 consecutive values starting at element i (i % 8 == 0, pointer 16-byte aligned)
 __device__ __forceinline__ void load8_f16(const __half *p, size_t i, float (&o)[8]) {
     const uint4 raw = *reinterpret_cast<const uint4 *>(p + i);
@@ -86,6 +73,119 @@ __device__ __forceinline__ void store8_f16(__half *p, size_t i, const float (&o)
 __device__ __forceinline__ void store8_f32(float *p, size_t i, const float (&o)[8]) {
     *reinterpret_cast<float4 *>(p + i) = make_float4(o[0], o[1], o[2], o[3]);
     *reinterpret_cast<float4 *>(p + i + 4) = make_float4(o[4], o[5], o[6], o[7]);
+}
+
+// Walsh-Hadamard transform of n = 1024*E values held in the registers of a 1024-thread CTA.
+// In : thread (warp w, lane l) holds elements (w*32 + l)*E + r, r < E   (E consecutive values).
+// Out: thread (w, l) holds elements (l*32 + w)*E + r                      (warp and lane swapped).
+// Butterflies over the low log2(E) index bits run in registers, over the 5 lane bits with shuffles; one
+// pass through shared memory (buf: 32*(32E+4) floats; rows padded by 4 words so that 16-byte accesses of
+// 8 lanes cover all banks) swaps the warp and lane bits, then the shuffles run again.  Contains one barrier.
+template <int E>
+__device__ __forceinline__ void fwht_regs(float (&v)[E], float *buf) {
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+#pragma unroll
+    for (int s = 1; s < E; s <<= 1)
+#pragma unroll
+        for (int k = 0; k < E; k++)
+            if (!(k & s)) { const float a = v[k], b = v[k | s]; v[k] = a + b; v[k | s] = a - b; }
+#pragma unroll
+    for (int bit = 1; bit < 32; bit <<= 1)
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const float o = __shfl_xor_sync(kFullMask, v[k], bit);
+            v[k] = (l & bit) ? o - v[k] : v[k] + o;
+        }
+    constexpr int kRow = 32 * E + 4;
+    float *dst = buf + w * kRow + l * E;
+    if constexpr (E >= 4) {
+#pragma unroll
+        for (int k = 0; k < E; k += 4) *reinterpret_cast<float4 *>(dst + k) = make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < E; k++) dst[k] = v[k];
+    }
+    __syncthreads();
+    const float *src = buf + l * kRow + w * E;
+    if constexpr (E >= 4) {
+#pragma unroll
+        for (int k = 0; k < E; k += 4) {
+            const float4 q = *reinterpret_cast<const float4 *>(src + k);
+            v[k] = q.x; v[k + 1] = q.y; v[k + 2] = q.z; v[k + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < E; k++) v[k] = src[k];
+    }
+#pragma unroll
+    for (int bit = 1; bit < 32; bit <<= 1)
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const float o = __shfl_xor_sync(kFullMask, v[k], bit);
+            v[k] = (l & bit) ? o - v[k] : v[k] + o;
+        }
+}
+
+// E consecutive values starting at element i (i % E == 0, pointers aligned to E elements)
+template <int E>
+__device__ __forceinline__ void loadE_f16(const __half *p, size_t i, float (&o)[E]) {
+    if constexpr (E == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p + i);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+        o[0] = __low2float(h[0]); o[1] = __high2float(h[0]); o[2] = __low2float(h[1]); o[3] = __high2float(h[1]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < E; k += 8) {
+            float t[8];
+            load8_f16(p, i + k, t);
+#pragma unroll
+            for (int q = 0; q < 8; q++) o[k + q] = t[q];
+        }
+    }
+}
+template <int E>
+__device__ __forceinline__ void loadE_f32(const float *p, size_t i, float (&o)[E], bool bypass_l1) {
+#pragma unroll
+    for (int k = 0; k < E; k += 4) {
+        const float4 *q = reinterpret_cast<const float4 *>(p + i + k);
+        const float4 a = bypass_l1 ? __ldcg(q) : *q;
+        o[k] = a.x; o[k + 1] = a.y; o[k + 2] = a.z; o[k + 3] = a.w;
+    }
+}
+template <int E>
+__device__ __forceinline__ void storeE_f16(__half *p, size_t i, const float (&o)[E]) {
+    if constexpr (E == 4) {
+        uint2 raw;
+        __half2 *h = reinterpret_cast<__half2 *>(&raw);
+        h[0] = __floats2half2_rn(o[0], o[1]); h[1] = __floats2half2_rn(o[2], o[3]);
+        *reinterpret_cast<uint2 *>(p + i) = raw;
+    } else {
+#pragma unroll
+        for (int k = 0; k < E; k += 8) {
+            float t[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) t[q] = o[k + q];
+            store8_f16(p, i + k, t);
+        }
+    }
+}
+template <int E>
+__device__ __forceinline__ void storeE_f32(float *p, size_t i, const float (&o)[E]) {
+#pragma unroll
+    for (int k = 0; k < E; k += 4) *reinterpret_cast<float4 *>(p + i + k) = make_float4(o[k], o[k + 1], o[k + 2], o[k + 3]);
+}
+
+// Sum over the CTA (scratch: one float per warp).  Contains two barriers.
+__device__ __forceinline__ float block_sum(float x, float *scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(kFullMask, x, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += scratch[w];
+    return t;
 }
 
 // SwiGLU product as fp16 tensors would compute it: silu(gate) rounded to fp16, product rounded to fp16.

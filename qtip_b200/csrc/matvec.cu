@@ -294,6 +294,67 @@ __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, i
     return o;
 }
 
+// Fused input side for n = 1024*E (E = 4, 8, 16): a thread owns E consecutive values, everything up to the
+// Walsh-Hadamard transform stays in registers (see fwht_regs), the result goes to xs in fragment order.
+template <int E>
+__device__ __forceinline__ void fused_input_regs(const FusedIn &I, int n, uint4 *xs, float *buf, float *warp_sums) {
+    const size_t j = (size_t)threadIdx.x * E;
+    float v[E], rs[E], wn[E], gt[E], sg[E];
+    loadE_f16<E>(I.x_raw, j, v);                     // all operand vectors are requested before any is used
+    if (I.residual) loadE_f16<E>(I.residual, j, rs);
+    if (I.norm_weight) loadE_f16<E>(I.norm_weight, j, wn);
+    if (I.gate) loadE_f16<E>(I.gate, j, gt);
+    if (I.sign_in) loadE_f16<E>(I.sign_in, j, sg);
+    if (I.residual) {
+#pragma unroll
+        for (int k = 0; k < E; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));   // fp16 residual stream
+        if (I.residual_out && blockIdx.x == 0) storeE_f16<E>(I.residual_out, j, v);
+    }
+    if (I.norm_weight) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < E; k++) ss += v[k] * v[k];
+        const float r = rsqrtf(block_sum(ss, warp_sums) / (float)n + I.eps);
+#pragma unroll
+        for (int k = 0; k < E; k++) v[k] = __half2float(__hmul(__float2half_rn(wn[k]), __float2half_rn(v[k] * r)));  // LlamaRMSNorm
+    }
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+        if (I.gate) v[k] = swiglu_fp16(gt[k], v[k]);
+        if (I.sign_in) v[k] *= sg[k];
+    }
+    fwht_regs<E>(v, buf);
+    // this thread now holds elements (lane*32 + warp)*E + r
+    const int i0 = ((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
+#pragma unroll
+    for (int k = 0; k < E; k += 2) {
+        const int wi = (i0 + k) >> 1, blk = wi >> 4, w = wi & 15;   // 16 words per 32-column block
+        reinterpret_cast<__half2 *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = __floats2half2_rn(v[k] * I.scale, v[k + 1] * I.scale);
+    }
+}
+
+// Fused output side for m = 1024*E, run by the CTA that finished last.
+template <int E>
+__device__ __forceinline__ void fused_output_regs(const FusedOut &O, const float *out, int m, int bs, float *buf) {
+    const size_t j = (size_t)threadIdx.x * E;
+    const size_t i0 = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;   // ownership after the transform
+    float sg[E];
+    if (O.sign_out) loadE_f32<E>(O.sign_out, i0, sg, false);
+    for (int b = 0; b < bs; b++) {
+        float v[E];
+        loadE_f32<E>(out + (size_t)b * m, j, v, true);
+        fwht_regs<E>(v, buf);
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            v[k] *= O.scale;
+            if (O.sign_out) v[k] *= sg[k];
+        }
+        if (O.dtype == QTIP_F16) storeE_f16<E>(static_cast<__half *>(O.final), (size_t)b * m + i0, v);
+        else storeE_f32<E>(static_cast<float *>(O.final), (size_t)b * m + i0, v);
+        __syncthreads();
+    }
+}
+
 // XS: x is staged once per CTA in shared memory, permuted so that a lane's four B-fragment words of
 // a block are one 16-byte load; otherwise they are read from global memory (L1-resident) per block.
 // DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
@@ -363,6 +424,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
             // the whole prologue costs one L2 round trip, not one per array.
             const FusedIn &I = P.in;
+            if (n == 4096) fused_input_regs<4>(I, n, xs, fscratch, sh->warp_sums);
+            else if (n == 8192) fused_input_regs<8>(I, n, xs, fscratch, sh->warp_sums);
+            else {
             const int nvec = n >> 3;
             float ss = 0.f;
             for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
@@ -415,6 +479,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int blk = i >> 4, w = i & 15;
                 const __half2 h = __floats2half2_rn(fscratch[pad(2 * i)] * I.scale, fscratch[pad(2 * i + 1)] * I.scale);
                 reinterpret_cast<__half2 *>(xs)[blk * 16 + (w & 3) * 4 + (w >> 2)] = h;
+            }
             }
         } else {
             // 4 words (8 values) per thread and trip
@@ -504,6 +569,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (sh->is_last) {
             __threadfence();
             float *f = reinterpret_cast<float *>(lut);   // the table is no longer needed
+            if (m == 4096) fused_output_regs<4>(P.ep, out, m, bs, f);
+            else if (m == 8192) fused_output_regs<8>(P.ep, out, m, bs, f);
+            else if (m == 16384) fused_output_regs<16>(P.ep, out, m, bs, f);
+            else {
             int p = 0;
             while ((1 << p) < m) p++;
             const int mvec = m >> 3;
@@ -533,6 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     else store8_f32(static_cast<float *>(P.ep.final), (size_t)b * m + j, y);
                 }
                 __syncthreads();
+            }
             }
             if (threadIdx.x == 0) *done_counter = 0;  // leave the workspace ready for the next call
         }

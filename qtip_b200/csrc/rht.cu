@@ -51,6 +51,55 @@ __device__ __forceinline__ void store8(void *p, int dtype, size_t i, const float
     else store8_f32(static_cast<float *>(p), i, o);
 }
 
+// Power-of-two n = 1024*E with vector-aligned buffers: a thread owns E consecutive values and the whole
+// row stays in registers (fwht_regs); shared memory is used for one transpose only.
+template <int E>
+__device__ __forceinline__ void rht_regs(const RhtArgs &a, float *buf, float *scratch) {
+    const int n = a.n;
+    const long row = blockIdx.y;
+    const size_t sign_off = (size_t)(row % a.sign_rep) * n;
+    const size_t in_off = (size_t)row * a.in_row_stride, out_off = (size_t)row * n;
+    const size_t j = (size_t)threadIdx.x * E;
+    const size_t jo = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;   // ownership after the transform
+    float v[E], rs[E], wn[E], gt[E], sg[E], so[E];
+    if (a.in_dtype == QTIP_F16) loadE_f16<E>(static_cast<const __half *>(a.in), in_off + j, v);
+    else loadE_f32<E>(static_cast<const float *>(a.in), in_off + j, v, false);
+    if (a.residual) loadE_f16<E>(a.residual, in_off + j, rs);
+    if (a.norm_weight) loadE_f16<E>(a.norm_weight, j, wn);
+    if (a.gate) loadE_f16<E>(a.gate, in_off + j, gt);
+    if (a.sign_in) {
+        if (a.sign_in_dtype == QTIP_F16) loadE_f16<E>(static_cast<const __half *>(a.sign_in), sign_off + j, sg);
+        else loadE_f32<E>(static_cast<const float *>(a.sign_in), sign_off + j, sg, false);
+    }
+    if (a.sign_out) loadE_f32<E>(a.sign_out, sign_off + jo, so, false);
+    if (a.residual) {
+#pragma unroll
+        for (int k = 0; k < E; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));
+        if (a.residual_out && (a.in_row_stride != 0 || row == 0)) storeE_f16<E>(a.residual_out, in_off + j, v);
+    }
+    if (a.norm_weight) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < E; k++) ss += v[k] * v[k];
+        const float r = rsqrtf(block_sum(ss, scratch) / (float)n + a.eps);
+#pragma unroll
+        for (int k = 0; k < E; k++) v[k] = __half2float(__hmul(__float2half_rn(wn[k]), __float2half_rn(v[k] * r)));
+    }
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+        if (a.gate) v[k] = swiglu_fp16(gt[k], v[k]);
+        if (a.sign_in) v[k] *= sg[k];
+    }
+    fwht_regs<E>(v, buf);
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+        v[k] *= a.scale;
+        if (a.sign_out) v[k] *= so[k];
+    }
+    if (a.out_dtype == QTIP_F16) storeE_f16<E>(static_cast<__half *>(a.out), out_off + jo, v);
+    else storeE_f32<E>(static_cast<float *>(a.out), out_off + jo, v);
+}
+
 __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     extern __shared__ __align__(16) float sm[];
     const int n = a.n, kfac = a.kfac;
@@ -86,6 +135,11 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool vec = a.vec_ok;
+    if (kfac == 1 && vec && (n == 4096 || n == 8192)) {
+        if (n == 4096) rht_regs<4>(a, v, scratch);
+        else rht_regs<8>(a, v, scratch);
+        return;
+    }
     const bool write_res = a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0);
     float ss = 0.f;
     if (vec) {
