@@ -195,7 +195,8 @@ int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long 
 int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, void *cache_v, const int *pos,
                         int n_heads, int n_kv_heads, int head_dim, float theta, void *stream);
 
-/* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128.
+/* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128;
+ * q and the caches 16-byte aligned.
  * Replaces the scaled_dot_product_attention call of LlamaSdpaAttention.forward (model/llama.py:884-891)
  * for a single new token. */
 int qtip_attn_decode(void *out, const void *q, const void *cache_k, const void *cache_v, const int *pos, int n_heads,

@@ -44,61 +44,137 @@ __global__ void rope_kv_kernel(__half *__restrict__ q, const __half *__restrict_
     }
 }
 
-// One CTA per query head, 8 warps; warp w scans cache positions w, w+8, ... <= pos with an online
-// softmax, lanes split the head dimension (hd = 128: 4 values per lane); partial results of the
-// warps are merged through shared memory.  out: (n_heads, hd) fp16.
-constexpr int kAttnWarps = 8;
+// One CTA per query head, 512 threads = 32 groups of 16 lanes; a lane owns 8 of the 128 head dimensions
+// (one 16-byte load per cache row), a group owns cache positions g, g+32, ...  The cache is read in
+// batches of 8 rows per group with all loads of a batch in flight at once: at decode lengths the kernel
+// is a handful of L2 round trips, not one per position.  Per chunk of kAttnChunk positions:
+//   scores -> shared memory, chunk maximum, p = exp(s - max) and its sum, then the weighted sum of V
+// (whose first batch is requested before the two block-wide reductions).  Chunks are merged with the
+// usual running maximum / denominator.  out: (n_heads, hd) fp16.
+constexpr int kAttnThreads = 512, kAttnGroups = kAttnThreads / 16, kAttnChunk = 2048, kAttnBatch = 8;
 
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__device__ __forceinline__ void unpack8(const uint4 &r, float (&f)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { f[2 * i] = __low2float(h[i]); f[2 * i + 1] = __high2float(h[i]); }
+}
+
+__global__ void __launch_bounds__(kAttnThreads)
     attn_decode_kernel(__half *__restrict__ out, const __half *__restrict__ q, const __half *__restrict__ cache_k,
                        const __half *__restrict__ cache_v, const int *__restrict__ pos_ptr, int n_heads, int n_kv,
                        float scale) {
-    constexpr int hd = 128;
+    constexpr int hd = 128, G = kAttnGroups, U = kAttnBatch;
+    __shared__ float sc[kAttnChunk];
+    __shared__ float red_max[kAttnThreads / 32], red_sum[kAttnThreads / 32];
+    __shared__ float accs[G][hd + 4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, kvh = head / (n_heads / n_kv);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, grp = tid >> 4, sub = tid & 15;
     const int ctx = *pos_ptr + 1;
     const size_t row = (size_t)n_kv * hd;
-    float qv[4];
-    {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(q + (size_t)head * hd + lane * 4);
-        const __half2 a = *reinterpret_cast<const __half2 *>(&raw.x), b = *reinterpret_cast<const __half2 *>(&raw.y);
-        qv[0] = __low2float(a) * scale; qv[1] = __high2float(a) * scale;
-        qv[2] = __low2float(b) * scale; qv[3] = __high2float(b) * scale;
-    }
-    float mx = -INFINITY, den = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int t = warp; t < ctx; t += kAttnWarps) {
-        const size_t off = (size_t)t * row + (size_t)kvh * hd + lane * 4;
-        const uint2 kr = *reinterpret_cast<const uint2 *>(cache_k + off);
-        const uint2 vr = *reinterpret_cast<const uint2 *>(cache_v + off);
-        const __half2 k0 = *reinterpret_cast<const __half2 *>(&kr.x), k1 = *reinterpret_cast<const __half2 *>(&kr.y);
-        float s = qv[0] * __low2float(k0) + qv[1] * __high2float(k0) + qv[2] * __low2float(k1) + qv[3] * __high2float(k1);
+    float qv[8];
+    unpack8(__ldg(reinterpret_cast<const uint4 *>(q + (size_t)head * hd + sub * 8)), qv);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(kFullMask, s, o);
-        const float nm = fmaxf(mx, s);
-        const float corr = __expf(mx - nm), pr = __expf(s - nm);
-        const __half2 v0 = *reinterpret_cast<const __half2 *>(&vr.x), v1 = *reinterpret_cast<const __half2 *>(&vr.y);
-        acc[0] = acc[0] * corr + pr * __low2float(v0); acc[1] = acc[1] * corr + pr * __high2float(v0);
-        acc[2] = acc[2] * corr + pr * __low2float(v1); acc[3] = acc[3] * corr + pr * __high2float(v1);
-        den = den * corr + pr;
-        mx = nm;
-    }
-    __shared__ float s_mx[kAttnWarps], s_den[kAttnWarps], s_acc[kAttnWarps][hd];
-    if (lane == 0) { s_mx[warp] = mx; s_den[warp] = den; }
+    for (int i = 0; i < 8; i++) qv[i] *= scale;
+    const __half *kb = cache_k + (size_t)kvh * hd + sub * 8, *vb = cache_v + (size_t)kvh * hd + sub * 8;
+
+    float m_run = -INFINITY, d_run = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int c0 = 0; c0 < ctx; c0 += kAttnChunk) {
+        const int cn = min(kAttnChunk, ctx - c0);
+        // ---- scores of the chunk
+        float lmax = -INFINITY;
+        // the trip count and every shuffle are uniform over the CTA: a warp holds two groups whose
+        // positions may fall on different sides of cn, so validity is a predicate, never a branch
+        // around a warp-wide shuffle
+        for (int tb = 0; tb < cn; tb += U * G) {
+            uint4 kr[U];
 #pragma unroll
-    for (int i = 0; i < 4; i++) s_acc[warp][lane * 4 + i] = acc[i];
-    __syncthreads();
-    if (threadIdx.x < hd) {
-        float gm = -INFINITY;
-        for (int w = 0; w < kAttnWarps; w++) gm = fmaxf(gm, s_mx[w]);
-        float d = 0.f, a = 0.f;
-        for (int w = 0; w < kAttnWarps; w++) {
-            const float c = (s_mx[w] == -INFINITY) ? 0.f : __expf(s_mx[w] - gm);
-            d += s_den[w] * c;
-            a += s_acc[w][threadIdx.x] * c;
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                kr[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (t < cn) kr[u] = __ldg(reinterpret_cast<const uint4 *>(kb + (size_t)(c0 + t) * row));
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                float kf[8], s = 0.f;
+                unpack8(kr[u], kf);
+#pragma unroll
+                for (int i = 0; i < 8; i++) s = fmaf(qv[i], kf[i], s);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(kFullMask, s, o);
+                if (t < cn) {
+                    if (sub == 0) sc[t] = s;
+                    lmax = fmaxf(lmax, s);
+                }
+            }
         }
-        out[(size_t)head * hd + threadIdx.x] = __float2half_rn(a / d);
+        // first batch of V rows: in flight during the reductions below
+        uint4 vr[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int t = grp + u * G;
+            if (t < cn) vr[u] = __ldg(reinterpret_cast<const uint4 *>(vb + (size_t)(c0 + t) * row));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
+        if (lane == 0) red_max[warp] = lmax;
+        __syncthreads();
+        float cmax = red_max[0];
+#pragma unroll
+        for (int w = 1; w < kAttnThreads / 32; w++) cmax = fmaxf(cmax, red_max[w]);
+        const float m_new = fmaxf(m_run, cmax);
+        const float corr = __expf(m_run - m_new);      // 0 for the first chunk
+        float lsum = 0.f;
+        for (int t = tid; t < cn; t += kAttnThreads) {
+            const float pr = __expf(sc[t] - m_new);
+            sc[t] = pr;
+            lsum += pr;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(kFullMask, lsum, o);
+        if (lane == 0) red_sum[warp] = lsum;
+        __syncthreads();
+        float csum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnThreads / 32; w++) csum += red_sum[w];
+        d_run = d_run * corr + csum;
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] *= corr;
+        // ---- weighted sum of V
+        for (int tb = 0; tb < cn; tb += U * G) {
+            uint4 cur[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) cur[u] = vr[u];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + U * G + grp + u * G;
+                if (t < cn) vr[u] = __ldg(reinterpret_cast<const uint4 *>(vb + (size_t)(c0 + t) * row));
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                if (t < cn) {
+                    float vf[8];
+                    unpack8(cur[u], vf);
+                    const float pr = sc[t];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) acc[i] = fmaf(pr, vf[i], acc[i]);
+                }
+            }
+        }
+        __syncthreads();    // sc and the reduction slots are reused by the next chunk
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) accs[grp][sub * 8 + i] = acc[i];
+    __syncthreads();
+    if (tid < hd) {
+        float a = 0.f;
+#pragma unroll
+        for (int g = 0; g < G; g++) a += accs[g][tid];
+        out[(size_t)head * hd + tid] = __float2half_rn(a / d_run);
     }
 }
 
@@ -137,8 +213,8 @@ extern "C" int qtip_attn_decode(void *out, const void *q, const void *cache_k, c
                                 int n_heads, int n_kv_heads, int head_dim, void *stream) {
     if (!out || !q || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
     if (head_dim != 128 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
-    if (!aligned(q, 8) || !aligned(cache_k, 8) || !aligned(cache_v, 8)) return QTIP_ERR_ALIGNMENT;
-    return launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream),
+    if (!aligned(q, 16) || !aligned(cache_k, 16) || !aligned(cache_v, 16)) return QTIP_ERR_ALIGNMENT;
+    return launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(kAttnThreads), static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(out), static_cast<const __half *>(q), static_cast<const __half *>(cache_k),
                       static_cast<const __half *>(cache_v), pos, n_heads, n_kv_heads, 1.0f / sqrtf((float)head_dim));
 }

@@ -196,3 +196,26 @@ def test_decompress_gemm(K, m, n, bs):
     assert rel_l2(y.cpu().numpy(), want.cpu().numpy()) < 1e-5
     y2 = ops.decompress_gemm(codes, x, tl, K, m, n)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ctx", [1, 7, 200, 257, 2048, 2049, 5000])
+@pytest.mark.parametrize("heads", [(8, 8), (16, 2)])
+def test_attn_decode_matches_fp32_softmax(ctx, heads):
+    """Single-query attention over a cache of `ctx` rows against an fp32 torch reference (tolerance:
+    fp16 rounding of the output, 2e-3 absolute on values of order 1)."""
+    n_heads, n_kv = heads
+    hd = 128
+    g = torch.Generator(device="cuda").manual_seed(ctx * 31 + n_heads)
+    q = torch.randn(n_heads, hd, generator=g, device="cuda").half()
+    ck = torch.randn(ctx + 3, n_kv * hd, generator=g, device="cuda").half()
+    cv = torch.randn(ctx + 3, n_kv * hd, generator=g, device="cuda").half()
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+    out = torch.empty(n_heads, hd, dtype=torch.float16, device="cuda")
+    ops.attn_decode(out, q, ck, cv, pos, n_heads, n_kv, hd)
+    rep = n_heads // n_kv
+    k = ck[:ctx].float().view(ctx, n_kv, hd).repeat_interleave(rep, dim=1)     # (ctx, heads, hd)
+    v = cv[:ctx].float().view(ctx, n_kv, hd).repeat_interleave(rep, dim=1)
+    s = torch.einsum("hd,thd->ht", q.float(), k) / hd ** 0.5
+    ref = torch.einsum("ht,thd->hd", torch.softmax(s, dim=-1), v)
+    torch.testing.assert_close(out.float(), ref, atol=2e-3, rtol=2e-3)
