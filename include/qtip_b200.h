@@ -96,6 +96,9 @@ int qtip_decompress_gemm(float *out, const void *codes, const void *x, const voi
  *   input side  (in_raw != NULL; needs bs == 1 and n a power of two <= 16384): every CTA computes
  *       x = fp16( H_n^T( sign_in * [silu(gate) *] [RMSNorm]( in_raw [+ residual] ) ) * in_scale )
  *       itself; residual_out (if given) receives in_raw + residual; norm_weight / gate / residual optional.
+ *       With in_y != NULL (n = 4096 or 8192) in_raw is not read: the value it stands for is computed on the
+ *       fly as fp16( in_y_sign * H_n(in_y) * in_y_scale ), i.e. the output side of the PRODUCER linear
+ *       (whose raw y is in_y) is deferred into this launch instead of running in the producer's last CTA.
  *   matvec      y (bs, m) fp32 = x @ decode(codes)^T, always written.
  *   output side (out != NULL; needs m a power of two <= 16384): the CTA that finishes last computes
  *       out = sign_out * H_m(y) * out_scale  (fp16 or fp32).
@@ -121,6 +124,9 @@ typedef struct qtip_linear_desc {
     int out_dtype;
     const float *sign_out;        /* (m) fp32 or NULL */
     float out_scale;
+    const float *in_y;            /* (n) fp32 raw output of the producer linear, or NULL */
+    const float *in_y_sign;       /* (n) fp32, the producer's sign_out; or NULL */
+    float in_y_scale;             /* the producer's out_scale */
 } qtip_linear_desc;
 int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream);
 
@@ -194,6 +200,17 @@ int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long 
  * model/cache_utils.py:1147-1193) for a single new token. */
 int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, void *cache_v, const int *pos,
                         int n_heads, int n_kv_heads, int head_dim, float theta, void *stream);
+
+/* qtip_rope_kv_append with the output side of the q / k / v linears in front of it: y_q / y_k / y_v are the raw
+ * fp32 results of the three matvecs (e.g. the y of a qtip_linear_fused launch without fused output side); the
+ * kernel computes fp16( sign * H(y) * scale ) - the tail of BitshiftLinear.forward, lib/codebook/bitshift.py:465-471
+ * - then rotates q (written to q_out) and k and appends k, v to the caches (model/llama.py:797-898,
+ * model/cache_utils.py:1147-1193).  n_heads*head_dim and n_kv_heads*head_dim in {1024, 2048, 4096, 8192, 16384};
+ * all pointers 16-byte aligned; sign_* (fp32) may be NULL. */
+int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
+                              const float *sign_k, const float *sign_v, float scale_q, float scale_kv, void *cache_k,
+                              void *cache_v, const int *pos, int n_heads, int n_kv_heads, int head_dim, float theta,
+                              void *stream);
 
 /* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128;
  * q and the caches 16-byte aligned.

@@ -20,7 +20,7 @@ class LinearDesc(ctypes.Structure):
     _fields_ = [("y", _vp), ("codes", _vp), ("tlut", _vp), ("x", _vp), ("workspace", _vp), ("workspace_bytes", _sz),
                 ("in_raw", _vp), ("residual", _vp), ("residual_out", _vp), ("norm_weight", _vp), ("gate", _vp),
                 ("sign_in", _vp), ("in_scale", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("sign_out", _vp),
-                ("out_scale", _f)]
+                ("out_scale", _f), ("in_y", _vp), ("in_y_sign", _vp), ("in_y_scale", _f)]
 
 
 # name -> (restype, argtypes); mirrors include/qtip_b200.h
@@ -40,6 +40,7 @@ SIGNATURES = {
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,
                             _vp]),
     "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }
 

@@ -5,6 +5,7 @@
 // LlamaSdpaAttention.forward upstream (model/llama.py:797-898, model/cache_utils.py:1147-1193).
 // The position is read from device memory so a captured graph can be replayed for every token.
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace qtip {
 namespace {
@@ -41,6 +42,70 @@ __global__ void rope_kv_kernel(__half *__restrict__ q, const __half *__restrict_
             cache_v[crow + (size_t)kh * hd + i] = v[(size_t)kh * hd + i];
             cache_v[crow + (size_t)kh * hd + i + half] = v[(size_t)kh * hd + i + half];
         }
+    }
+}
+
+// rope_kv_kernel with the output side of the q/k/v linears in front of it: CTA 0 / 1 / 2 takes the raw
+// matvec result y_q / y_k / y_v (fp32), applies sign * H(y) * scale in registers (fwht_regs), rounds to
+// fp16 as the linear's output tensor would be, and then rotates / appends as above.  The matvec launch
+// then needs no last-CTA epilogue.  Widths are 1024*E, E in {1, 2, 4, 8, 16}.
+struct QkvPostArgs {
+    const float *y[3];
+    const float *sv[3];
+    float scale[3];
+    int width[3];
+    __half *q_out, *cache_k, *cache_v;
+    const int *pos;
+    int n_heads, n_kv, hd;
+    float log2_theta;
+};
+
+template <int E>
+__device__ __forceinline__ void qkv_transform(const QkvPostArgs &a, int which, float *buf, float *vals) {
+    const size_t jA = (size_t)threadIdx.x * E;
+    const size_t jB = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
+    float v[E], sg[E];
+    if (a.sv[which]) loadE_f32<E>(a.sv[which], jB, sg, false);     // a weight: requested before the wait
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    loadE_f32<E>(a.y[which], jA, v, true);
+    fwht_regs<E>(v, buf);
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+        v[k] *= a.scale[which];
+        if (a.sv[which]) v[k] *= sg[k];
+        vals[jB + k] = __half2float(__float2half_rn(v[k]));
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024) qkv_post_kernel(const QkvPostArgs a) {
+    extern __shared__ __align__(16) float sm_post[];
+    const int which = blockIdx.x, width = a.width[which];
+    float *buf = sm_post, *vals = sm_post + width + 128;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    switch (width >> 10) {
+        case 1: qkv_transform<1>(a, which, buf, vals); break;
+        case 2: qkv_transform<2>(a, which, buf, vals); break;
+        case 4: qkv_transform<4>(a, which, buf, vals); break;
+        case 8: qkv_transform<8>(a, which, buf, vals); break;
+        default: qkv_transform<16>(a, which, buf, vals); break;
+    }
+    const int pos = *a.pos, hd = a.hd, half = hd >> 1;
+    const size_t crow = (size_t)pos * a.n_kv * hd;
+    if (which == 2) {
+        for (int e = threadIdx.x * 2; e < width; e += blockDim.x * 2)
+            *reinterpret_cast<__half2 *>(a.cache_v + crow + e) = __floats2half2_rn(vals[e], vals[e + 1]);
+        return;
+    }
+    __half *dst = which == 0 ? a.q_out : a.cache_k + crow;
+    for (int idx = threadIdx.x; idx < (width >> 1); idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const float inv_freq = exp2f(-a.log2_theta * (float)(2 * i) / (float)hd);
+        float sn, cs;
+        sincosf((float)pos * inv_freq, &sn, &cs);
+        const float x0 = vals[head * hd + i], x1 = vals[head * hd + i + half];
+        dst[(size_t)head * hd + i] = __float2half_rn(x0 * cs - x1 * sn);
+        dst[(size_t)head * hd + i + half] = __float2half_rn(x1 * cs + x0 * sn);
     }
 }
 
@@ -207,6 +272,47 @@ extern "C" int qtip_rope_kv_append(void *q, const void *k, const void *v, void *
                       static_cast<__half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
                       static_cast<__half *>(cache_k), static_cast<__half *>(cache_v), pos, n_heads, n_kv_heads, head_dim,
                       log2f(theta));
+}
+
+extern "C" int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, const float *y_v,
+                                         const float *sign_q, const float *sign_k, const float *sign_v, float scale_q,
+                                         float scale_kv, void *cache_k, void *cache_v, const int *pos, int n_heads,
+                                         int n_kv_heads, int head_dim, float theta, void *stream) {
+    if (!q_out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
+    const int wq = n_heads * head_dim, wkv = n_kv_heads * head_dim;
+    auto ok_width = [](int w) { return w == 1024 || w == 2048 || w == 4096 || w == 8192 || w == 16384; };
+    if (!ok_width(wq) || !ok_width(wkv)) return QTIP_ERR_BAD_SHAPE;
+    const void *ptrs[] = {q_out, y_q, y_k, y_v, sign_q, sign_k, sign_v, cache_k, cache_v};
+    for (const void *p : ptrs)
+        if (p && !aligned(p, 16)) return QTIP_ERR_ALIGNMENT;
+    QkvPostArgs a = {};
+    a.y[0] = y_q; a.y[1] = y_k; a.y[2] = y_v;
+    a.sv[0] = sign_q; a.sv[1] = sign_k; a.sv[2] = sign_v;
+    a.scale[0] = scale_q; a.scale[1] = scale_kv; a.scale[2] = scale_kv;
+    a.width[0] = wq; a.width[1] = wkv; a.width[2] = wkv;
+    a.q_out = static_cast<__half *>(q_out); a.cache_k = static_cast<__half *>(cache_k); a.cache_v = static_cast<__half *>(cache_v);
+    a.pos = pos; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.hd = head_dim; a.log2_theta = log2f(theta);
+    const size_t smem = (size_t)(2 * wq + 128) * sizeof(float);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    QTIP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(qkv_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (2 * 16384 + 128) * 4));
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(3);
+    cfg.blockDim = dim3(1024);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, qkv_post_kernel, a));
+    return check_launch();
 }
 
 extern "C" int qtip_attn_decode(void *out, const void *q, const void *cache_k, const void *cache_v, const int *pos,

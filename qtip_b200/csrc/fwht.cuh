@@ -126,7 +126,8 @@ __device__ __forceinline__ void fwht_regs(float (&v)[E], float *buf) {
         }
 }
 
-// E consecutive values starting at element i (i % E == 0, pointers aligned to E elements)
+// E consecutive values starting at element i (i % E == 0, pointers aligned to E elements).
+// The fp32 load takes E = 1, 2 or a multiple of 4; the fp16 forms and the stores E = 4 or a multiple of 8.
 template <int E>
 __device__ __forceinline__ void loadE_f16(const __half *p, size_t i, float (&o)[E]) {
     if constexpr (E == 4) {
@@ -145,11 +146,19 @@ __device__ __forceinline__ void loadE_f16(const __half *p, size_t i, float (&o)[
 }
 template <int E>
 __device__ __forceinline__ void loadE_f32(const float *p, size_t i, float (&o)[E], bool bypass_l1) {
+    if constexpr (E == 1) {
+        o[0] = bypass_l1 ? __ldcg(p + i) : p[i];
+    } else if constexpr (E == 2) {
+        const float2 *q = reinterpret_cast<const float2 *>(p + i);
+        const float2 a = bypass_l1 ? __ldcg(q) : *q;
+        o[0] = a.x; o[1] = a.y;
+    } else {
 #pragma unroll
-    for (int k = 0; k < E; k += 4) {
-        const float4 *q = reinterpret_cast<const float4 *>(p + i + k);
-        const float4 a = bypass_l1 ? __ldcg(q) : *q;
-        o[k] = a.x; o[k + 1] = a.y; o[k + 2] = a.z; o[k + 3] = a.w;
+        for (int k = 0; k < E; k += 4) {
+            const float4 *q = reinterpret_cast<const float4 *>(p + i + k);
+            const float4 a = bypass_l1 ? __ldcg(q) : *q;
+            o[k] = a.x; o[k + 1] = a.y; o[k + 2] = a.z; o[k + 3] = a.w;
+        }
     }
 }
 template <int E>

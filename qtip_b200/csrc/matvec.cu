@@ -264,6 +264,10 @@ struct FusedIn {    // x_raw != nullptr: x = fp16( H^T( sign_in * [silu(gate) *]
     const __half *x_raw, *residual, *norm_weight, *gate, *sign_in;
     __half *residual_out;
     float scale, eps;
+    // y_prev != nullptr: x_raw is not read; it is fp16(prev_sign * H(y_prev) * prev_scale), the deferred
+    // output side of the linear that produced y_prev
+    const float *y_prev, *prev_sign;
+    float prev_scale;
 };
 struct FusedOut {   // final != nullptr: final = sign_out * H(out) * scale, computed by the last CTA to finish
     void *final;
@@ -298,13 +302,33 @@ __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, i
 // Walsh-Hadamard transform stays in registers (see fwht_regs), the result goes to xs in fragment order.
 template <int E>
 __device__ __forceinline__ void fused_input_regs(const FusedIn &I, int n, uint4 *xs, float *buf, float *warp_sums) {
-    const size_t j = (size_t)threadIdx.x * E;
+    // ownership of the E consecutive values a thread works on: tid*E ("A"), or, after one fwht_regs,
+    // (lane*32 + warp)*E ("B").  The transform maps A to B and B to A, every other step is element-wise or
+    // a sum over everything, so the deferred-producer path simply does its element-wise work in B.
+    const bool deferred = I.y_prev != nullptr;
+    const size_t jA = (size_t)threadIdx.x * E;
+    const size_t jB = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
+    const size_t j = deferred ? jB : jA;
     float v[E], rs[E], wn[E], gt[E], sg[E];
-    loadE_f16<E>(I.x_raw, j, v);                     // all operand vectors are requested before any is used
+    // all operand vectors are requested before any is used
+    if (deferred) loadE_f32<E>(I.y_prev, jA, v, true);
+    else loadE_f16<E>(I.x_raw, j, v);
     if (I.residual) loadE_f16<E>(I.residual, j, rs);
     if (I.norm_weight) loadE_f16<E>(I.norm_weight, j, wn);
     if (I.gate) loadE_f16<E>(I.gate, j, gt);
     if (I.sign_in) loadE_f16<E>(I.sign_in, j, sg);
+    if (deferred) {
+        float ps[E];
+        if (I.prev_sign) loadE_f32<E>(I.prev_sign, jB, ps, false);
+        fwht_regs<E>(v, buf);
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            v[k] *= I.prev_scale;
+            if (I.prev_sign) v[k] *= ps[k];
+            v[k] = __half2float(__float2half_rn(v[k]));      // the producer's output is an fp16 tensor
+        }
+        __syncthreads();                                       // buf is used again below
+    }
     if (I.residual) {
 #pragma unroll
         for (int k = 0; k < E; k++) v[k] = __half2float(__float2half_rn(v[k] + rs[k]));   // fp16 residual stream
@@ -324,8 +348,7 @@ __device__ __forceinline__ void fused_input_regs(const FusedIn &I, int n, uint4 
         if (I.sign_in) v[k] *= sg[k];
     }
     fwht_regs<E>(v, buf);
-    // this thread now holds elements (lane*32 + warp)*E + r
-    const int i0 = ((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
+    const int i0 = (int)(deferred ? jA : jB);                  // ownership after the transform
 #pragma unroll
     for (int k = 0; k < E; k += 2) {
         const int wi = (i0 + k) >> 1, blk = wi >> 4, w = wi & 15;   // 16 words per 32-column block
@@ -419,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
-        if (P.in.x_raw) {
+        if (P.in.x_raw || P.in.y_prev) {
             // fused input side (bs == 1, n a power of two): every CTA transforms the activation itself.
             // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
             // the whole prologue costs one L2 round trip, not one per array.
@@ -816,18 +839,20 @@ extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K
     for (int i = 0; i < count; i++) {
         const qtip_linear_desc &d = descs[i];
         if (!d.tlut) return QTIP_ERR_BAD_ARG;
-        const bool fin = d.in_raw != nullptr, fout = d.out != nullptr;
+        const bool fin = d.in_raw != nullptr || d.in_y != nullptr, fout = d.out != nullptr;
         if (i > 0 && fin != fused_in) return QTIP_ERR_BAD_ARG;   // all or none: the shared-memory layout is per launch
         fused_in = fin;
-        const void *x = fin ? d.in_raw : d.x;
+        const void *x = d.in_y ? (const void *)d.in_y : fin ? d.in_raw : d.x;
         int st = check_common(d.y, d.codes, x, K, m, n, bs, d.workspace, d.workspace_bytes);
         if (st != QTIP_OK) return st;
         if (!aligned(d.tlut, 4)) return QTIP_ERR_ALIGNMENT;
         if (fin && (bs != 1 || (n & (n - 1)) || n > 16384)) return QTIP_ERR_BAD_SHAPE;
+        if (d.in_y && n != 4096 && n != 8192) return QTIP_ERR_BAD_SHAPE;
         if (fout && ((m & (m - 1)) || m > 16384)) return QTIP_ERR_BAD_SHAPE;
         if (fout && d.out_dtype != QTIP_F16 && d.out_dtype != QTIP_F32) return QTIP_ERR_BAD_ARG;
         {
             const void *vecs[] = {d.in_raw, d.residual, d.residual_out, d.norm_weight, d.gate, d.sign_in, d.out, d.sign_out,
+                                  d.in_y, d.in_y_sign,
                                   (fin || fout) ? (const void *)d.y : nullptr};
             for (const void *q : vecs)
                 if (q && !aligned(q, 16)) return QTIP_ERR_ALIGNMENT;
@@ -843,6 +868,7 @@ extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K
             P.in.residual_out = static_cast<__half *>(d.residual_out);
             P.in.norm_weight = static_cast<const __half *>(d.norm_weight); P.in.gate = static_cast<const __half *>(d.gate);
             P.in.sign_in = static_cast<const __half *>(d.sign_in); P.in.scale = d.in_scale; P.in.eps = d.eps;
+            P.in.y_prev = d.in_y; P.in.prev_sign = d.in_y_sign; P.in.prev_scale = d.in_y_scale;
         }
         if (fout) { P.ep.final = d.out; P.ep.sign_out = d.sign_out; P.ep.scale = d.out_scale; P.ep.dtype = d.out_dtype; }
     }

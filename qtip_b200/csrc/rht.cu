@@ -33,6 +33,8 @@ struct RhtArgs {
     int out_dtype, in_dtype, sign_in_dtype;
     int n, p, sign_rep, kfac, transpose;
     int rpc;             // hadK output rows per CTA (4, 8 or 16)
+    int part_offset;     // float offset in shared memory of the partial-product buffer (short rows only)
+    int sgn_offset;      // float offset of the staged sign_out slice (short rows only, else 0)
     int vec_ok;          // every buffer is 16-byte aligned and n, strides are multiples of 8: 8-wide loads / stores
     float scale, eps;
 };
@@ -49,6 +51,19 @@ __device__ __forceinline__ void load8(const void *p, int dtype, size_t i, float 
 __device__ __forceinline__ void store8(void *p, int dtype, size_t i, const float (&o)[8]) {
     if (dtype == QTIP_F16) store8_f16(static_cast<__half *>(p), i, o);
     else store8_f32(static_cast<float *>(p), i, o);
+}
+
+// 8 values from one (fp16) or two (fp32) raw 16-byte registers
+__device__ __forceinline__ void unpack_raw(const uint4 *r, int dtype, float (&o)[8]) {
+    if (dtype == QTIP_F16) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(r);
+#pragma unroll
+        for (int k = 0; k < 4; k++) { o[2 * k] = __low2float(h[k]); o[2 * k + 1] = __high2float(h[k]); }
+    } else {
+        const float *f = reinterpret_cast<const float *>(r);
+#pragma unroll
+        for (int k = 0; k < 8; k++) o[k] = f[k];
+    }
 }
 
 // Power-of-two n = 1024*E with vector-aligned buffers: a thread owns E consecutive values and the whole
@@ -131,10 +146,21 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
             hs[idx] = sgn;
         }
     }
+    // short rows: this CTA's slice of sign_out (a weight) is copied to shared memory asynchronously now,
+    // so the final store does not wait for it
+    const bool vec = a.vec_ok;
+    const bool sign_staged = kfac > 1 && vec && a.sign_out && a.sgn_offset > 0 && ((n / kfac) & 7) == 0;
+    if (sign_staged) {
+        const int len_ = n / kfac;
+        const float *src = a.sign_out + sign_off + (size_t)i0 * len_;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(sm + a.sgn_offset);
+        for (int c = threadIdx.x; c < (rows_here * len_) >> 2; c += blockDim.x)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * 16), "l"(src + c * 4) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const bool vec = a.vec_ok;
     if (kfac == 1 && vec && (n == 4096 || n == 8192)) {
         if (n == 4096) rht_regs<4>(a, v, scratch);
         else rht_regs<8>(a, v, scratch);
@@ -142,7 +168,47 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     }
     const bool write_res = a.residual_out && blockIdx.x == 0 && (a.in_row_stride != 0 || row == 0);
     float ss = 0.f;
-    if (vec) {
+    if (vec && !a.residual && !a.norm_weight) {
+        // two 8-value vectors per thread and trip, every load of both requested before the first use
+        const int nvec = n >> 3;
+        for (int j0 = threadIdx.x; j0 < nvec; j0 += 2 * blockDim.x) {
+            const int jv[2] = {j0, j0 + (int)blockDim.x};
+            uint4 xr[2][2], gr[2], sr[2][2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                if (jv[u] >= nvec) continue;
+                const size_t j = (size_t)jv[u] * 8;
+                if (a.in_dtype == QTIP_F16) xr[u][0] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(a.in) + in_off + j);
+                else {
+                    const uint4 *q = reinterpret_cast<const uint4 *>(static_cast<const float *>(a.in) + in_off + j);
+                    xr[u][0] = q[0]; xr[u][1] = q[1];
+                }
+                if (a.gate) gr[u] = *reinterpret_cast<const uint4 *>(a.gate + in_off + j);
+                if (a.sign_in) {
+                    if (a.sign_in_dtype == QTIP_F16) sr[u][0] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(a.sign_in) + sign_off + j);
+                    else {
+                        const uint4 *q = reinterpret_cast<const uint4 *>(static_cast<const float *>(a.sign_in) + sign_off + j);
+                        sr[u][0] = q[0]; sr[u][1] = q[1];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                if (jv[u] >= nvec) continue;
+                const int j = jv[u] * 8;
+                float x[8], gt[8], sg[8];
+                unpack_raw(xr[u], a.in_dtype, x);
+                if (a.gate) unpack_raw(&gr[u], QTIP_F16, gt);
+                if (a.sign_in) unpack_raw(sr[u], a.sign_in_dtype, sg);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    if (a.gate) x[k] = swiglu_fp16(gt[k], x[k]);
+                    if (a.sign_in) x[k] *= sg[k];
+                    v[pad(j + k)] = x[k];
+                }
+            }
+        }
+    } else if (vec) {
         // a thread owns 8 consecutive values; all operand vectors are requested before any is used
         for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
             float x[8], rs[8], gt[8], sg[8];
@@ -238,42 +304,71 @@ __global__ void __launch_bounds__(kRhtThreads) rht_kernel(const RhtArgs a) {
     // The products stay in registers until every thread has finished reading v; the rows are then written over
     // the start of v (the host guarantees at most 4 items per thread).
     const int items = (rpc >> 2) * len;
-    float acc[4][4];
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int idx = threadIdx.x + t * blockDim.x;
-#pragma unroll
-        for (int r = 0; r < 4; r++) acc[t][r] = 0.f;
-        if (idx < items) {
-            const int j = idx & (len - 1), il = (idx >> p) * 4;
+    float *wbuf = v;
+    if (items * 2 <= (int)blockDim.x) {
+        // short rows: the k range is cut into blockDim.x / items slices so that every thread takes part;
+        // the slices' partial products meet in `part` ([slice][row][column]) and are summed below
+        const int slices = blockDim.x / items, kper = (kfac + slices - 1) / slices;
+        const int sl = threadIdx.x / items, item = threadIdx.x - sl * items;
+        const int j = item & (len - 1), il = (item >> p) * 4;
+        const int k0 = sl * kper, k1 = min(kfac, k0 + kper);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
-            for (int k = 0; k < kfac; k++) {
-                const float x = v[pad(k * len + j)];
-                const float4 h = *reinterpret_cast<const float4 *>(hs + k * rpc + il);
-                acc[t][0] = fmaf(h.x, x, acc[t][0]); acc[t][1] = fmaf(h.y, x, acc[t][1]);
-                acc[t][2] = fmaf(h.z, x, acc[t][2]); acc[t][3] = fmaf(h.w, x, acc[t][3]);
+        for (int k = k0; k < k1; k++) {
+            const float x = v[pad(k * len + j)];
+            const float4 h = *reinterpret_cast<const float4 *>(hs + k * rpc + il);
+            acc[0] = fmaf(h.x, x, acc[0]); acc[1] = fmaf(h.y, x, acc[1]);
+            acc[2] = fmaf(h.z, x, acc[2]); acc[3] = fmaf(h.w, x, acc[3]);
+        }
+        float *part = a.part_offset + sm;
+#pragma unroll
+        for (int r = 0; r < 4; r++) part[(sl * rpc + il + r) * len + j] = acc[r];
+        __syncthreads();
+        for (int e = threadIdx.x; e < rpc * len; e += blockDim.x) {
+            float t = 0.f;
+            for (int q = 0; q < slices; q++) t += part[q * rpc * len + e];
+            wbuf[pad(e)] = t;
+        }
+        __syncthreads();
+    } else {
+        float acc[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const int idx = threadIdx.x + t * blockDim.x;
+#pragma unroll
+            for (int r = 0; r < 4; r++) acc[t][r] = 0.f;
+            if (idx < items) {
+                const int j = idx & (len - 1), il = (idx >> p) * 4;
+#pragma unroll 4
+                for (int k = 0; k < kfac; k++) {
+                    const float x = v[pad(k * len + j)];
+                    const float4 h = *reinterpret_cast<const float4 *>(hs + k * rpc + il);
+                    acc[t][0] = fmaf(h.x, x, acc[t][0]); acc[t][1] = fmaf(h.y, x, acc[t][1]);
+                    acc[t][2] = fmaf(h.z, x, acc[t][2]); acc[t][3] = fmaf(h.w, x, acc[t][3]);
+                }
             }
         }
-    }
-    __syncthreads();
-    float *wbuf = v;
+        __syncthreads();
 #pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int idx = threadIdx.x + t * blockDim.x;
-        if (idx < items) {
-            const int j = idx & (len - 1), il = (idx >> p) * 4;
+        for (int t = 0; t < 4; t++) {
+            const int idx = threadIdx.x + t * blockDim.x;
+            if (idx < items) {
+                const int j = idx & (len - 1), il = (idx >> p) * 4;
 #pragma unroll
-            for (int r = 0; r < 4; r++) wbuf[pad((il + r) * len + j)] = acc[t][r];
+                for (int r = 0; r < 4; r++) wbuf[pad((il + r) * len + j)] = acc[t][r];
+            }
         }
+        __syncthreads();
     }
-    __syncthreads();
+    if (sign_staged) asm volatile("cp.async.wait_all;" ::: "memory");   // made visible by the barriers below
     fwht_shared(wbuf, rpc * len, p);
     const int total = rows_here * len;
     if (vec && (len & 7) == 0) {
         for (int e = threadIdx.x * 8; e < total; e += blockDim.x * 8) {
             const size_t o = (size_t)i0 * len + e;      // rows of this CTA are contiguous in the output
             float y[8], sg[8];
-            if (a.sign_out) load8_f32(a.sign_out, sign_off + o, sg);
+            if (sign_staged) load8_f32(sm + a.sgn_offset, e, sg);
+            else if (a.sign_out) load8_f32(a.sign_out, sign_off + o, sg);
 #pragma unroll
             for (int k = 0; k < 8; k++) {
                 y[k] = wbuf[pad(e + k)] * scale;
@@ -306,13 +401,20 @@ int launch_rht(RhtArgs a, long rows, void *stream) {
     a.p = p;
     // rows of the factor matrix per CTA: 8, or 4 when a row is long - a thread keeps at most 4 x 4 products
     // in registers, so (rpc / 4) * len <= 4 * kRhtThreads
-    auto smem_for = [&](int rpc) {
-        return ((size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)rpc * a.kfac : 0) + 32 +
-                (a.kfac > 1 ? (size_t)a.kfac * ((a.kfac + 31) / 32) : 0)) * sizeof(float);
-    };
     a.rpc = len >= 1024 ? 4 : 8;
     if (a.kfac > 1 && (a.rpc / 4) * len > 4 * kRhtThreads) return QTIP_ERR_BAD_SHAPE;
-    const size_t smem = smem_for(a.rpc);
+    // floats: values (padded) + alignment slack, signs of this CTA's rows, block_sum scratch, the bit matrix,
+    // and for short rows the partial products of the k slices (4 per thread)
+    size_t words = (size_t)a.n + (a.n >> 5) + 8 + (a.kfac > 1 ? (size_t)a.rpc * a.kfac : 0) + 32 +
+                   (a.kfac > 1 ? (size_t)a.kfac * ((a.kfac + 31) / 32) : 0);
+    words = (words + 3) & ~(size_t)3;
+    a.part_offset = (int)words;
+    if (a.kfac > 1 && (a.rpc / 4) * len * 2 <= kRhtThreads) {
+        words += 4 * kRhtThreads;
+        a.sgn_offset = (int)words;
+        words += (size_t)a.rpc * len;
+    }
+    const size_t smem = words * sizeof(float);
     {
         const void *ptrs[] = {a.out, a.in, a.residual, a.residual_out, a.gate, a.sign_in, a.sign_out, a.norm_weight};
         bool ok = (a.n % 8 == 0) && (a.in_row_stride % 8 == 0);

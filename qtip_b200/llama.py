@@ -138,6 +138,10 @@ class QtipLlama:
         self.fuse_in_h, self.fuse_in_hl, self.fuse_in_m = fin(s.hidden), fin(H), fin(MLP)
         fout = lambda d: pow2(d) and d <= 16384  # noqa: E731
         self.fuse_out_h, self.fuse_out_hl, self.fuse_out_kv, self.fuse_out_m = fout(s.hidden), fout(H), fout(KV), fout(MLP)
+        # deferred output sides: the Hadamard transform + sign of o_proj / down_proj runs in the prologue of the
+        # NEXT launch (which needs the register transform: 4096 or 8192 wide), that of q/k/v in the rotary kernel
+        self.defer_h = tp == 1 and self.fuse_in_h and s.hidden in (4096, 8192)
+        self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
         self.graph = None
         self.n_launches_per_step = None   # counted while the step runs (library launches only)
 
@@ -159,7 +163,9 @@ class QtipLlama:
             if fused_in is None:
                 d["x"] = xs_or_raw[i]
             else:
-                d.update(in_raw=fused_in["in_raw"], residual=fused_in.get("residual"), norm_weight=fused_in.get("norm_weight"),
+                d.update(in_raw=fused_in.get("in_raw"), in_y=fused_in.get("in_y"), in_y_sign=fused_in.get("in_y_sign"),
+                         in_y_scale=fused_in.get("in_y_scale", 1.0),
+                         residual=fused_in.get("residual"), norm_weight=fused_in.get("norm_weight"),
                          gate=fused_in.get("gate"), sign_in=fused_in["sign_ins"][i], in_scale=fused_in["in_scale"],
                          eps=self.shape.rms_eps)
                 if i == 0:
@@ -181,21 +187,26 @@ class QtipLlama:
         tp1 = self.tp == 1
         y_q, y_k, y_v = self.y_qkv[:H], self.y_qkv[H:H + KV], self.y_qkv[H + KV:]
         q, k, v = self.qkv[:H], self.qkv[H:H + KV], self.qkv[H + KV:]
+        delta_src = dict(in_raw=self.delta)      # where the pending residual update comes from
+        last = len(self.layers) - 1
         for li, L in enumerate(self.layers):
             # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v (column-parallel)
-            if self.fuse_in_h and self.fuse_out_hl and self.fuse_out_kv:
-                fin = dict(in_raw=self.delta, residual=res_a, residual_out=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32)
+            if self.fuse_in_h and (self.defer_qkv or (self.fuse_out_hl and self.fuse_out_kv)):
+                dq = self.defer_qkv
+                fin = dict(delta_src, residual=res_a, residual_out=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32)
                 if H == KV:
                     self._linears([L["q"], L["k"], L["v"]], None, [y_q, y_k, y_v], s.hidden, H,
-                                  fused_in=dict(fin, sign_ins=[L["q"].SU, L["k"].SU, L["v"].SU]), outs=[q, k, v],
+                                  fused_in=dict(fin, sign_ins=[L["q"].SU, L["k"].SU, L["v"].SU]), outs=None if dq else [q, k, v],
                                   sign_outs=[L["q"].SV32, L["k"].SV32, L["v"].SV32], out_scale=inv_hl)
                 else:
-                    self._linears([L["q"]], None, [y_q], s.hidden, H, fused_in=dict(fin, sign_ins=[L["q"].SU]), outs=[q],
-                                  sign_outs=[L["q"].SV32], out_scale=inv_hl)
+                    self._linears([L["q"]], None, [y_q], s.hidden, H, fused_in=dict(fin, sign_ins=[L["q"].SU]),
+                                  outs=None if dq else [q], sign_outs=[L["q"].SV32], out_scale=inv_hl)
                     fin2 = dict(in_raw=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32, sign_ins=[L["k"].SU, L["v"].SU])
-                    self._linears([L["k"], L["v"]], None, [y_k, y_v], s.hidden, KV, fused_in=fin2, outs=[k, v],
+                    self._linears([L["k"], L["v"]], None, [y_k, y_v], s.hidden, KV, fused_in=fin2, outs=None if dq else [k, v],
                                   sign_outs=[L["k"].SV32, L["v"].SV32], out_scale=inv_kv)
             else:
+                dq = False
+                assert "in_raw" in delta_src
                 xh = self.xh_qkv
                 ops.rht_fused(self.delta, 3, s.hidden, xh, in_row_stride=0, residual=res_a, residual_out=res_b,
                               norm_weight=L["ln1"], eps=s.rms_eps, sign_in=L["SU_qkv"], hadk_bits=bits[self.kf_h],
@@ -209,12 +220,18 @@ class QtipLlama:
                     sv = L["SV_kv"] = torch.cat([L["k"].SV32, L["v"].SV32]).contiguous()
                 ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=bits[self.kf_kv],
                               kfac=self.kf_kv, scale=inv_kv)
-            ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                               s.head_dim, s.rope_theta)
+            if dq:
+                ops.rope_kv_append_fused(q, y_q, y_k, y_v, L["q"].SV32, L["k"].SV32, L["v"].SV32, inv_hl, inv_kv,
+                                         self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                                         s.head_dim, s.rope_theta)
+            else:
+                ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                                   s.head_dim, s.rope_theta)
             ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
                             s.head_dim)
             # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
-            fuse_out = tp1 and self.fuse_out_h
+            defer = self.defer_h
+            fuse_out = tp1 and self.fuse_out_h and not defer
             if self.fuse_in_hl:
                 self._linears([L["o"]], None, [self.y_h], H, s.hidden,
                               fused_in=dict(in_raw=self.attn, sign_ins=[L["o"].SU], in_scale=inv_hl / 32),
@@ -224,14 +241,18 @@ class QtipLlama:
                               transpose=True, scale=inv_hl / 32)
                 self._linears([L["o"]], [self.xh_o], [self.y_h], H, s.hidden, outs=[self.delta] if fuse_out else None,
                               sign_outs=[L["o"].SV32], out_scale=inv_h)
-            if not fuse_out:
-                self._all_reduce(self.y_h)
-                ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=bits[self.kf_h],
-                              kfac=self.kf_h, scale=inv_h)
+            if defer:
+                delta_src = dict(in_y=self.y_h, in_y_sign=L["o"].SV32, in_y_scale=inv_h)
+            else:
+                delta_src = dict(in_raw=self.delta)
+                if not fuse_out:
+                    self._all_reduce(self.y_h)
+                    ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["o"].SV32, hadk_bits=bits[self.kf_h],
+                                  kfac=self.kf_h, scale=inv_h)
             # ---- MLP block: res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up (column-parallel)
             y_g, y_u = self.y_gu[:MLP], self.y_gu[MLP:]
             if self.fuse_in_h:
-                fin = dict(in_raw=self.delta, residual=res_b, residual_out=res_a, norm_weight=L["ln2"], in_scale=inv_h / 32,
+                fin = dict(delta_src, residual=res_b, residual_out=res_a, norm_weight=L["ln2"], in_scale=inv_h / 32,
                            sign_ins=[L["gate"].SU, L["up"].SU])
                 fo = self.fuse_out_m
                 self._linears([L["gate"], L["up"]], None, [y_g, y_u], s.hidden, MLP, fused_in=fin,
@@ -249,7 +270,8 @@ class QtipLlama:
                 ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
                               kfac=self.kf_m, scale=inv_m)
             # ---- down_proj (row-parallel), input silu(gate) * up
-            fuse_out = tp1 and self.fuse_out_h
+            defer = self.defer_h and li != last       # the last layer's result is read by the final norm
+            fuse_out = tp1 and self.fuse_out_h and not defer
             if self.fuse_in_m:
                 self._linears([L["down"]], None, [self.y_h], MLP, s.hidden,
                               fused_in=dict(in_raw=self.gu[MLP:], gate=self.gu[:MLP], sign_ins=[L["down"].SU], in_scale=inv_m / 32),
@@ -260,10 +282,14 @@ class QtipLlama:
                               hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
                 self._linears([L["down"]], [xd], [self.y_h], MLP, s.hidden, outs=[self.delta] if fuse_out else None,
                               sign_outs=[L["down"].SV32], out_scale=inv_h)
-            if not fuse_out:
-                self._all_reduce(self.y_h)
-                ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
-                              kfac=self.kf_h, scale=inv_h)
+            if defer:
+                delta_src = dict(in_y=self.y_h, in_y_sign=L["down"].SV32, in_y_scale=inv_h)
+            else:
+                delta_src = dict(in_raw=self.delta)
+                if not fuse_out:
+                    self._all_reduce(self.y_h)
+                    ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
+                                  kfac=self.kf_h, scale=inv_h)
         # ---- final norm, lm_head, sampler (torch)
         h = (res_a + self.delta).float()
         h = (h * torch.rsqrt(h.pow(2).mean() + s.rms_eps)).half() * self.ln_f

@@ -264,6 +264,19 @@ def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim
     launch_count += 1
 
 
+def rope_kv_append_fused(q_out, y_q, y_k, y_v, sign_q, sign_k, sign_v, scale_q, scale_kv, cache_k, cache_v, pos, n_heads,
+                         n_kv_heads, head_dim, theta=10000.0):
+    """qtip_rope_kv_append_fused: output side of the q/k/v linears + rotary embedding + cache append, one launch."""
+    ptr = lambda t: 0 if t is None else t.data_ptr()   # noqa: E731
+    st = _lib.load().qtip_rope_kv_append_fused(q_out.data_ptr(), y_q.data_ptr(), y_k.data_ptr(), y_v.data_ptr(), ptr(sign_q),
+                                               ptr(sign_k), ptr(sign_v), float(scale_q), float(scale_kv), cache_k.data_ptr(),
+                                               cache_v.data_ptr(), pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta),
+                                               _stream())
+    _lib.check(st, "qtip_rope_kv_append_fused")
+    global launch_count
+    launch_count += 1
+
+
 def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
     st = _lib.load().qtip_attn_decode(out.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(),
                                       n_heads, n_kv_heads, head_dim, _stream())
@@ -276,16 +289,17 @@ def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
 def linear_fused(descs, K, m, n, bs=1):
     """qtip_linear_fused: one launch for up to four same-shape linears, transforms optionally fused.
     `descs` is a list of dicts with tensor values for the fields of qtip_linear_desc (missing = NULL):
-    y, codes, tlut, x, workspace, in_raw, residual, residual_out, norm_weight, gate, sign_in, out, sign_out
-    plus floats in_scale, eps, out_scale."""
+    y, codes, tlut, x, workspace, in_raw, residual, residual_out, norm_weight, gate, sign_in, out, sign_out, in_y,
+    in_y_sign plus floats in_scale, eps, out_scale, in_y_scale."""
     arr = (_lib.LinearDesc * len(descs))()
     for d, c in zip(descs, arr):
         for name in ("y", "codes", "tlut", "x", "workspace", "in_raw", "residual", "residual_out", "norm_weight", "gate",
-                     "sign_in", "out", "sign_out"):
+                     "sign_in", "out", "sign_out", "in_y", "in_y_sign"):
             t = d.get(name)
             setattr(c, name, None if t is None else t.data_ptr())
         c.workspace_bytes = d["workspace"].numel()
         c.in_scale, c.eps, c.out_scale = float(d.get("in_scale", 1.0)), float(d.get("eps", 0.0)), float(d.get("out_scale", 1.0))
+        c.in_y_scale = float(d.get("in_y_scale", 1.0))
         c.out_dtype = F16 if d.get("out") is None else _dtype_id(d["out"])
     st = _lib.load().qtip_linear_fused(arr, len(descs), K, m, n, bs, _stream())
     _lib.check(st, "qtip_linear_fused")

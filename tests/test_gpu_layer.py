@@ -240,6 +240,63 @@ def test_linear_fused_matches_three_kernel_path(K):
         assert torch.equal(d["y"].view(1, m), ops.decompress_matvec(d["codes"], x, d["tlut"], K, m, n))
 
 
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_linear_fused_deferred_producer_side(n):
+    """in_y: the producer's output side (sign * H(y) * scale, rounded to fp16) computed inside the consumer's
+    prologue must equal handing the consumer the materialised fp16 tensor."""
+    import math
+    from qtip_b200 import _lib
+    K, m = 2, 4096
+    lay = synth.make_layer(m, n, K, seed=900 + n)
+    g = torch.Generator().manual_seed(n)
+    y_prev = torch.randn(n, generator=g).to(DEV)                       # raw fp32 result of some producer linear
+    sv_prev = (torch.randn(n, generator=g).sign() * 0.37).to(DEV)
+    res = torch.randn(n, generator=g).half().to(DEV)
+    w = (1 + 0.1 * torch.randn(n, generator=g)).half().to(DEV)
+    codes, tl = t16(lay["codes"]), torch.from_numpy(lay["tlut"]).to(DEV)
+    SU = torch.from_numpy(lay["SU"]).to(DEV)
+    need = _lib.load().qtip_matvec_workspace_bytes(m, n, 1)
+    delta = ops.rht(y_prev.view(1, n), sign_out=sv_prev, scale=1 / math.sqrt(n), out_dtype=torch.float16).view(n)
+    common = dict(codes=codes, tlut=tl, residual=res, norm_weight=w, sign_in=SU, in_scale=1 / (math.sqrt(n) * 32), eps=1e-5)
+    a = dict(common, y=torch.zeros(m, device=DEV), workspace=torch.zeros(need, dtype=torch.uint8, device=DEV),
+             in_raw=delta, residual_out=torch.zeros(n, dtype=torch.float16, device=DEV))
+    b = dict(common, y=torch.zeros(m, device=DEV), workspace=torch.zeros(need, dtype=torch.uint8, device=DEV),
+             in_y=y_prev, in_y_sign=sv_prev, in_y_scale=1 / math.sqrt(n),
+             residual_out=torch.zeros(n, dtype=torch.float16, device=DEV))
+    ops.linear_fused([a], K, m, n, 1)
+    for _ in range(2):
+        ops.linear_fused([b], K, m, n, 1)
+        torch.cuda.synchronize()
+        # the two transforms sum in different orders: fp16 roundings of the intermediate may differ in the last bit
+        assert rel_l2(b["residual_out"].float().cpu().numpy(), a["residual_out"].float().cpu().numpy()) < 1e-3
+        assert rel_l2(b["y"].cpu().numpy(), a["y"].cpu().numpy()) < 2e-3
+
+
+@pytest.mark.parametrize("heads", [(32, 32), (32, 8), (64, 8)])
+def test_rope_kv_append_fused_matches_separate_launches(heads):
+    """qtip_rope_kv_append_fused == output-side RHT of q/k/v + qtip_rope_kv_append."""
+    import math
+    n_heads, n_kv = heads
+    hd, pos_v, maxpos = 128, 5, 8
+    H, KV = n_heads * hd, n_kv * hd
+    g = torch.Generator().manual_seed(n_heads * 100 + n_kv)
+    y = [torch.randn(w, generator=g).to(DEV) for w in (H, KV, KV)]
+    sv = [(torch.randn(w, generator=g).sign() * 0.5).to(DEV) for w in (H, KV, KV)]
+    pos = torch.tensor([pos_v], dtype=torch.int32, device=DEV)
+    q, k, v = [ops.rht(t.view(1, -1), sign_out=s_, scale=1 / math.sqrt(t.numel()), out_dtype=torch.float16).view(-1)
+               for t, s_ in zip(y, sv)]
+    ck, cv = [torch.zeros(maxpos, KV, dtype=torch.float16, device=DEV) for _ in range(2)]
+    ops.rope_kv_append(q, k, v, ck, cv, pos, n_heads, n_kv, hd, 10000.0)
+    q2 = torch.zeros(H, dtype=torch.float16, device=DEV)
+    ck2, cv2 = [torch.zeros(maxpos, KV, dtype=torch.float16, device=DEV) for _ in range(2)]
+    ops.rope_kv_append_fused(q2, y[0], y[1], y[2], sv[0], sv[1], sv[2], 1 / math.sqrt(H), 1 / math.sqrt(KV), ck2, cv2, pos,
+                             n_heads, n_kv, hd, 10000.0)
+    torch.cuda.synchronize()
+    for got, want in ((q2, q), (ck2, ck), (cv2, cv)):
+        assert rel_l2(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1e-3
+    assert torch.count_nonzero(ck2[:pos_v]) == 0 and torch.count_nonzero(ck2[pos_v + 1:]) == 0
+
+
 def test_quip_lib_op_under_graph_capture():
     """The torch op boundary (lib/codebook/__init__.py:68-93 upstream): eager call and CUDA-graph replay."""
     from qtip_b200 import codebook_ops
