@@ -188,6 +188,19 @@ int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long 
                    const void *sign_in, int sign_in_dtype, const float *sign_out, long n_signs,
                    const uint32_t *hadk_bits, int kfac, int transpose, float scale, void *stream);
 
+/* Everything between the gate/up matvecs and the down matvec of a Llama MLP for one token, in one launch
+ * (one 8-CTA cluster; the +-1 Hadamard factor runs on the tensor cores with the data split into an fp16 head and
+ * remainder):  out (n) fp16 = fp16( H^T( sign_down * silu(g) * u ) * scale_in ),
+ *   g = fp16( sign_gate * H(y_gate) * scale_out ),  u = fp16( sign_up * H(y_up) * scale_out ),
+ * i.e. the output side of gate_proj and up_proj (lib/codebook/bitshift.py:465-471), the SwiGLU product
+ * (model/llama.py:399-400) and the input side of down_proj (bitshift.py:428-441).  y_* are the raw fp32 matvec
+ * results, sign_gate / sign_up fp32, sign_down fp16, all (n) and 16-byte aligned; n = kfac * len with
+ * kfac > 1 from the table of qtip_rht and len in {32, 64, 128} (qtip_mlp_mid_supported tells, 1 = yes). */
+int qtip_mlp_mid_supported(int n, int kfac);
+int qtip_mlp_mid(void *out, const float *y_gate, const float *y_up, const float *sign_gate, const float *sign_up,
+                 const void *sign_down, const uint32_t *hadk_bits, int n, int kfac, float scale_out, float scale_in,
+                 void *stream);
+
 /* --------------------------------------------------------------------------------------------
  * Decode-loop support (batch 1): the per-token attention pieces between the QTIP linears, so that a
  * decode step is one CUDA graph of this library's launches.  fp16 tensors; `pos` points to the

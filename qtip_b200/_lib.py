@@ -39,6 +39,8 @@ SIGNATURES = {
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,
                             _vp]),
+    "qtip_mlp_mid_supported": (_i, [_i, _i]),
+    "qtip_mlp_mid": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp]),
     "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),

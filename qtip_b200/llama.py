@@ -142,6 +142,8 @@ class QtipLlama:
         # NEXT launch (which needs the register transform: 4096 or 8192 wide), that of q/k/v in the rotary kernel
         self.defer_h = tp == 1 and self.fuse_in_h and s.hidden in (4096, 8192)
         self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
+        # gate/up output side + SwiGLU + down input side as one cluster launch (widths with a Hadamard factor)
+        self.mid_fused = (not self.fuse_out_m) and (not self.fuse_in_m) and ops.mlp_mid_supported(MLP)
         self.graph = None
         self.n_launches_per_step = None   # counted while the step runs (library launches only)
 
@@ -266,7 +268,11 @@ class QtipLlama:
                               kfac=self.kf_h, transpose=True, scale=inv_h / 32)
                 self._matvec(L["gate"], xg[0], y_g)
                 self._matvec(L["up"], xg[1], y_u)
-            if not fo:
+            mid = self.mid_fused and not fo
+            if mid:
+                ops.mlp_mid(self.xh_d, y_g, y_u, L["gate"].SV32, L["up"].SV32, L["down"].SU, MLP, inv_m, inv_m / 32,
+                            hadk_bits=bits[self.kf_m])
+            elif not fo:
                 ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
                               kfac=self.kf_m, scale=inv_m)
             # ---- down_proj (row-parallel), input silu(gate) * up
@@ -278,8 +284,9 @@ class QtipLlama:
                               outs=[self.delta] if fuse_out else None, sign_outs=[L["down"].SV32], out_scale=inv_h)
             else:
                 xd = self.xh_d
-                ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
-                              hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
+                if not mid:
+                    ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
+                                  hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
                 self._linears([L["down"]], [xd], [self.y_h], MLP, s.hidden, outs=[self.delta] if fuse_out else None,
                               sign_outs=[L["down"].SV32], out_scale=inv_h)
             if defer:

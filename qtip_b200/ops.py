@@ -256,6 +256,33 @@ def rht_fused(x, rows, n, out, *, in_row_stride=None, residual=None, residual_ou
     return out
 
 
+def mlp_mid_supported(n):
+    """True when qtip_mlp_mid handles width n (a non-trivial Hadamard factor and a row length of 32..128)."""
+    k = had_factor(n)
+    return bool(k and k > 1 and _lib.load().qtip_mlp_mid_supported(int(n), int(k)))
+
+
+_mid_bits = {}
+
+
+def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scale_in, hadk_bits=None):
+    """qtip_mlp_mid: output side of gate/up + SwiGLU + input side of down_proj, one launch.  out: (n) fp16.
+    hadk_bits: packed signs of the factor matrix (pack_hadk); looked up and cached per device when omitted."""
+    k = had_factor(n)
+    if hadk_bits is None:
+        key = (k, str(out.device))
+        hadk_bits = _mid_bits.get(key)
+        if hadk_bits is None:
+            hadk_bits = _mid_bits[key] = pack_hadk(get_hadK(n)[0].to(out.device))
+    st = _lib.load().qtip_mlp_mid(out.data_ptr(), y_gate.data_ptr(), y_up.data_ptr(), sign_gate.data_ptr(), sign_up.data_ptr(),
+                                  sign_down.data_ptr(), hadk_bits.data_ptr(), int(n), int(k),
+                                  float(scale_out), float(scale_in), _stream())
+    _lib.check(st, "qtip_mlp_mid")
+    global launch_count
+    launch_count += 1
+    return out
+
+
 def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, theta=10000.0):
     st = _lib.load().qtip_rope_kv_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
                                          pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), _stream())

@@ -297,6 +297,38 @@ def test_rope_kv_append_fused_matches_separate_launches(heads):
     assert torch.count_nonzero(ck2[:pos_v]) == 0 and torch.count_nonzero(ck2[pos_v + 1:]) == 0
 
 
+@pytest.mark.parametrize("n", [11008, 5504, 1376, 3328])
+def test_mlp_mid_matches_two_rht_launches(n):
+    """qtip_mlp_mid (tensor-core Hadamard factor, one cluster launch) against the output-side RHT of gate and up
+    followed by the SwiGLU + input-side RHT of down_proj.  Widths: 172*64, 172*32, 172*8 (unsupported row length:
+    must be refused), 52*64."""
+    import math
+    g = torch.Generator().manual_seed(n)
+    y_g, y_u = [(torch.randn(n, generator=g) * 3).to(DEV) for _ in range(2)]
+    sv_g, sv_u = [(torch.randn(n, generator=g).sign() * 1.7).to(DEV) for _ in range(2)]
+    su = torch.randn(n, generator=g).sign().half().to(DEV)
+    out = torch.zeros(n, dtype=torch.float16, device=DEV)
+    if not ops.mlp_mid_supported(n):
+        assert n == 1376
+        with pytest.raises(RuntimeError):
+            ops.mlp_mid(out, y_g, y_u, sv_g, sv_u, su, n, 1 / math.sqrt(n), 1 / (32 * math.sqrt(n)))
+        return
+    hadK, kfac = ops.get_hadK(n)
+    bits = ops.hadk_bits_for(hadK, torch.device(DEV))
+    gu = torch.zeros(2, n, dtype=torch.float16, device=DEV)
+    ops.rht_fused(torch.stack([y_g, y_u]), 2, n, gu, sign_out=torch.cat([sv_g, sv_u]), hadk_bits=bits, kfac=kfac,
+                  scale=1 / math.sqrt(n))
+    want = torch.zeros(n, dtype=torch.float16, device=DEV)
+    ops.rht_fused(gu[1], 1, n, want, gate=gu[0], sign_in=su, hadk_bits=bits, kfac=kfac, transpose=True,
+                  scale=1 / (32 * math.sqrt(n)))
+    for _ in range(2):
+        out.zero_()
+        ops.mlp_mid(out, y_g, y_u, sv_g, sv_u, su, n, 1 / math.sqrt(n), 1 / (32 * math.sqrt(n)))
+        torch.cuda.synchronize()
+        # fp16 roundings of g, u may fall on the other side in a few places (different summation order)
+        assert rel_l2(out.float().cpu().numpy(), want.float().cpu().numpy()) < 2e-3
+
+
 def test_quip_lib_op_under_graph_capture():
     """The torch op boundary (lib/codebook/__init__.py:68-93 upstream): eager call and CUDA-graph replay."""
     from qtip_b200 import codebook_ops
