@@ -189,16 +189,22 @@ int qtip_rht_fused(void *out, int out_dtype, const void *in, int in_dtype, long 
                    const uint32_t *hadk_bits, int kfac, int transpose, float scale, void *stream);
 
 /* Everything between the gate/up matvecs and the down matvec of a Llama MLP for one token, in one launch
- * (one 8-CTA cluster; the +-1 Hadamard factor runs on the tensor cores with the data split into an fp16 head and
- * remainder):  out (n) fp16 = fp16( H^T( sign_down * silu(g) * u ) * scale_in ),
+ * (one cluster of 16 CTAs, or 8 where 16 cannot be co-scheduled; the +-1 Hadamard factor runs on the tensor cores):
+ *   out (n) fp16 = fp16( H^T( sign_down * silu(g) * u ) * scale_in ),
  *   g = fp16( sign_gate * H(y_gate) * scale_out ),  u = fp16( sign_up * H(y_up) * scale_out ),
  * i.e. the output side of gate_proj and up_proj (lib/codebook/bitshift.py:465-471), the SwiGLU product
  * (model/llama.py:399-400) and the input side of down_proj (bitshift.py:428-441).  y_* are the raw fp32 matvec
- * results, sign_gate / sign_up fp32, sign_down fp16, all (n) and 16-byte aligned; n = kfac * len with
- * kfac > 1 from the table of qtip_rht and len in {32, 64, 128} (qtip_mlp_mid_supported tells, 1 = yes). */
+ * results, sign_gate / sign_up fp32, sign_down fp16 with entries +-1, all (n) and 16-byte aligned;
+ * n = kfac * len with kfac > 1 from the table of qtip_rht and len in {32, 64, 128}
+ * (qtip_mlp_mid_supported tells, 1 = yes).  `table` (qtip_mlp_mid_table_bytes() bytes of device memory,
+ * 16-byte aligned) is derived from the packed factor matrix once, by qtip_mlp_mid_prepare on the same device,
+ * and can be kept for the life of the model.  The first call on a device queries the cluster occupancy and
+ * must happen outside stream capture. */
 int qtip_mlp_mid_supported(int n, int kfac);
+size_t qtip_mlp_mid_table_bytes(void);
+int qtip_mlp_mid_prepare(void *table, const uint32_t *hadk_bits, int n, int kfac, void *stream);
 int qtip_mlp_mid(void *out, const float *y_gate, const float *y_up, const float *sign_gate, const float *sign_up,
-                 const void *sign_down, const uint32_t *hadk_bits, int n, int kfac, float scale_out, float scale_in,
+                 const void *sign_down, const void *table, int n, int kfac, float scale_out, float scale_in,
                  void *stream);
 
 /* --------------------------------------------------------------------------------------------

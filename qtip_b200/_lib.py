@@ -40,6 +40,8 @@ SIGNATURES = {
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,
                             _vp]),
     "qtip_mlp_mid_supported": (_i, [_i, _i]),
+    "qtip_mlp_mid_table_bytes": (_sz, []),
+    "qtip_mlp_mid_prepare": (_i, [_vp, _vp, _i, _i, _vp]),
     "qtip_mlp_mid": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp]),
     "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),

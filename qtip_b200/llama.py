@@ -144,6 +144,7 @@ class QtipLlama:
         self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
         # gate/up output side + SwiGLU + down input side as one cluster launch (widths with a Hadamard factor)
         self.mid_fused = (not self.fuse_out_m) and (not self.fuse_in_m) and ops.mlp_mid_supported(MLP)
+        self.mid_table = ops.mlp_mid_table(MLP, dev, self.bits[self.kf_m]) if self.mid_fused else None
         self.graph = None
         self.n_launches_per_step = None   # counted while the step runs (library launches only)
 
@@ -271,7 +272,7 @@ class QtipLlama:
             mid = self.mid_fused and not fo
             if mid:
                 ops.mlp_mid(self.xh_d, y_g, y_u, L["gate"].SV32, L["up"].SV32, L["down"].SU, MLP, inv_m, inv_m / 32,
-                            hadk_bits=bits[self.kf_m])
+                            table=self.mid_table)
             elif not fo:
                 ops.rht_fused(self.y_gu, 2, MLP, self.gu, sign_out=L["SV_gu"], hadk_bits=bits[self.kf_m],
                               kfac=self.kf_m, scale=inv_m)

@@ -70,8 +70,9 @@ def plain_launches(m, n, K, bs, code, count, device="cuda:0"):
     torch.cuda.synchronize(device)
 
 
-def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0):
-    """Input-side transform (fp16 in, SwiGLU gate, signs, fp16 out) of `rows` rows of width n."""
+def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0, mid=False):
+    """Input-side transform (fp16 in, SwiGLU gate, signs, fp16 out) of `rows` rows of width n; mid=True times
+    qtip_mlp_mid (gate/up output side + SwiGLU + down input side) instead."""
     import math
     k = ops.had_factor(n)
     bits = None if k == 1 else ops.pack_hadk(ops.get_hadK(n)[0].to(device))
@@ -79,9 +80,13 @@ def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0):
     gate = torch.randn(rows, n, device=device).half()
     su = torch.ones(n, device=device, dtype=torch.float16)
     out = torch.empty(rows, n, device=device, dtype=torch.float16)
+    y_g, y_u, sv = (torch.randn(n, device=device) for _ in range(3))
 
     def launch():
-        ops.rht_fused(x, rows, n, out, gate=gate, sign_in=su, hadk_bits=bits, kfac=k, transpose=True, scale=1 / math.sqrt(n))
+        if mid:
+            ops.mlp_mid(out, y_g, y_u, sv, sv, su, n, 1 / math.sqrt(n), 1 / math.sqrt(n))
+        else:
+            ops.rht_fused(x, rows, n, out, gate=gate, sign_in=su, hadk_bits=bits, kfac=k, transpose=True, scale=1 / math.sqrt(n))
 
     if plain:
         for _ in range(plain):
@@ -112,6 +117,7 @@ def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--mlp-mid", default="", help="comma-separated widths: time qtip_mlp_mid")
     ap.add_argument("--rht", default="", help="comma-separated widths: time the transform kernel instead of the matvec")
     ap.add_argument("--shapes", default=LLAMA7B)
     ap.add_argument("--bits", default="2,3,4")
@@ -127,6 +133,12 @@ def main():
                                            "MEASURED_PEAKS.json")))["hbm_gbs"]
     except (OSError, KeyError):
         pass
+    if args.mlp_mid:
+        for n in (int(v) for v in args.mlp_mid.split(",")):
+            us = time_rht(n, plain=args.plain_launches, mid=True)
+            if us is not None:
+                print(f"mlp_mid n={n} (factor {ops.had_factor(n)}): {us:7.2f} us per launch (back-to-back launches in one graph)", flush=True)
+        return
     if args.rht:
         for n in (int(v) for v in args.rht.split(",")):
             us = time_rht(n, plain=args.plain_launches)

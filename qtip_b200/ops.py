@@ -262,20 +262,31 @@ def mlp_mid_supported(n):
     return bool(k and k > 1 and _lib.load().qtip_mlp_mid_supported(int(n), int(k)))
 
 
-_mid_bits = {}
+_mid_tables = {}
 
 
-def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scale_in, hadk_bits=None):
-    """qtip_mlp_mid: output side of gate/up + SwiGLU + input side of down_proj, one launch.  out: (n) fp16.
-    hadk_bits: packed signs of the factor matrix (pack_hadk); looked up and cached per device when omitted."""
+def mlp_mid_table(n, device, hadk_bits=None):
+    """Device table of qtip_mlp_mid_prepare for width n (cached per factor order and device)."""
     k = had_factor(n)
-    if hadk_bits is None:
-        key = (k, str(out.device))
-        hadk_bits = _mid_bits.get(key)
+    key = (k, str(device), None if hadk_bits is None else hadk_bits.data_ptr())
+    t = _mid_tables.get(key)
+    if t is None:
         if hadk_bits is None:
-            hadk_bits = _mid_bits[key] = pack_hadk(get_hadK(n)[0].to(out.device))
+            hadk_bits = pack_hadk(get_hadK(n)[0].to(device))
+        lib = _lib.load()
+        t = torch.zeros(lib.qtip_mlp_mid_table_bytes(), dtype=torch.uint8, device=device)
+        _lib.check(lib.qtip_mlp_mid_prepare(t.data_ptr(), hadk_bits.data_ptr(), int(n), int(k), _stream()), "qtip_mlp_mid_prepare")
+        _mid_tables[key] = t
+    return t
+
+
+def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scale_in, table=None):
+    """qtip_mlp_mid: output side of gate/up + SwiGLU + input side of down_proj, one launch.  out: (n) fp16.
+    table: mlp_mid_table(n, device); looked up (and built on first use, which allocates) when omitted."""
+    if table is None:
+        table = mlp_mid_table(n, out.device)
     st = _lib.load().qtip_mlp_mid(out.data_ptr(), y_gate.data_ptr(), y_up.data_ptr(), sign_gate.data_ptr(), sign_up.data_ptr(),
-                                  sign_down.data_ptr(), hadk_bits.data_ptr(), int(n), int(k),
+                                  sign_down.data_ptr(), table.data_ptr(), int(n), int(had_factor(n)),
                                   float(scale_out), float(scale_in), _stream())
     _lib.check(st, "qtip_mlp_mid")
     global launch_count
