@@ -238,7 +238,7 @@ def run_gpu(args):
     for _ in range(steps):
         model.token.copy_(h_tok, non_blocking=True)
         model.graph.replay()
-        h_out.copy_(model.next_token, non_blocking=True)
+        h_out.copy_(model.token, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         h_tok[0] = h_out[0]
     barrier()

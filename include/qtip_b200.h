@@ -213,6 +213,24 @@ int qtip_mlp_mid(void *out, const float *y_gate, const float *y_up, const float 
  * token position in device memory (read at run time, so a captured graph can be replayed).
  * ------------------------------------------------------------------------------------------ */
 
+/* Embedding lookup for one token: res (hidden) fp16 = embed[*token] (embed is (vocab, hidden) fp16, token a
+ * 64-bit index in device memory); delta (hidden) fp16 = 0.  Replaces embed_tokens of LlamaModel.forward
+ * (model/llama.py) for the decode loop.  hidden a multiple of 8, pointers 16-byte aligned. */
+int qtip_embed_token(void *res, void *delta, const void *embed, const long long *token, int hidden, void *stream);
+
+/* Final RMSNorm and the (unquantized, fp16) lm_head for one token:
+ * logits (vocab) fp32 = weight (vocab, hidden) @ fp16( norm_weight * fp16( RMSNorm(res + delta) ) ), the tail of
+ * LlamaForCausalLM.forward (model/llama.py).  An HBM-bound matrix-vector product; pointers 16-byte aligned. */
+int qtip_lm_head(float *logits, const void *res, const void *delta, const void *norm_weight, const void *weight,
+                 int hidden, int vocab, float eps, void *stream);
+
+/* Temperature / top-k sampling without a host synchronisation (eval/interactive_gen.py:15-40: logits_to_probs +
+ * multinomial_sample_one_no_sync): the top_k (<= 16) largest logits, softmax(top / temperature), one draw from a
+ * counter-based generator keyed by (seed, *pos).  Writes the token to *token and out_tokens[*pos + 1] and
+ * advances *pos (32-bit, device memory).  The draw is reproducible for a given seed but is not torch's stream. */
+int qtip_sample_top_k(long long *token, long long *out_tokens, int *pos, const float *logits, int vocab,
+                      float temperature, int top_k, unsigned long long seed, void *stream);
+
 /* Rotary embedding of q (n_heads, head_dim; in place) and k (n_kv_heads, head_dim), and append of the
  * rotated k and of v to the caches at row *pos (caches are (max_positions, n_kv_heads*head_dim)).
  * Replaces apply_rotary_pos_emb + StaticCache.update (model/llama.py:797-898,

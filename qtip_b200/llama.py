@@ -11,7 +11,7 @@ Llama-2-7B shape is 8 launches of this library's kernels:
     gate,up in one launch (residual add, RMSNorm, input transform fused)   their output transform (11008 = 172*64)
     input transform of down_proj with the SwiGLU product fused             down_proj (output transform fused)
 Widths that are not powers of two, and tensor-parallel row-parallel layers (all-reduce between matvec and
-output transform), fall back to separate transform launches.  The embedding lookup, the final norm, the fp16 lm_head and the sampler are plain torch ops.
+output transform), fall back to separate transform launches.  The embedding lookup, the final norm + fp16 lm_head and the sampler are three small launches of the library as well.
 """
 import math
 from dataclasses import dataclass
@@ -126,7 +126,7 @@ class QtipLlama:
         self.y_gu = torch.zeros(2 * MLP, **f32)
         self.gu = torch.zeros(2 * MLP, **f16)
         self.logits = torch.zeros(1, s.vocab, **f32)
-        self.next_token = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.sample_seed = seed
         self.out_tokens = torch.zeros(max_positions + 1, dtype=torch.int64, device=dev)
         need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
                    for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
@@ -183,8 +183,7 @@ class QtipLlama:
         s = self.shape
         H, KV, MLP = self.H, self.KV, self.MLP
         res_a, res_b = self.res
-        res_a.copy_(torch.index_select(self.embed, 0, self.token).view(-1))
-        self.delta.zero_()
+        ops.embed_token(res_a, self.delta, self.embed, self.token)
         inv_h, inv_hl, inv_m, inv_kv = (1 / math.sqrt(d) for d in (s.hidden, H, MLP, KV))
         bits = self.bits
         tp1 = self.tp == 1
@@ -298,23 +297,9 @@ class QtipLlama:
                     self._all_reduce(self.y_h)
                     ops.rht_fused(self.y_h, 1, s.hidden, self.delta, sign_out=L["down"].SV32, hadk_bits=bits[self.kf_h],
                                   kfac=self.kf_h, scale=inv_h)
-        # ---- final norm, lm_head, sampler (torch)
-        h = (res_a + self.delta).float()
-        h = (h * torch.rsqrt(h.pow(2).mean() + s.rms_eps)).half() * self.ln_f
-        self.logits.copy_(torch.matmul(h.view(1, -1), self.lm_head.T))
-        self._sample()
-        self.out_tokens.index_copy_(0, self.pos.to(torch.int64) + 1, self.next_token)
-        self.token.copy_(self.next_token)
-        self.pos.add_(1)
-
-    def _sample(self, temperature=0.6, top_k=5):
-        """temperature / top-k sampling without a host sync (eval/interactive_gen.py:15-40 upstream)."""
-        logits = self.logits / max(temperature, 1e-5)
-        v, _ = torch.topk(logits, top_k)
-        logits = torch.where(logits < v[:, -1:], torch.full_like(logits, -float("inf")), logits)
-        probs = torch.softmax(logits, dim=-1)
-        q = torch.empty_like(probs).exponential_(1)
-        self.next_token.copy_(torch.argmax(probs / q, dim=-1))
+        # ---- final norm + lm_head (fp16 weights, HBM-bound GEMV), sampler: token, out_tokens[pos + 1], pos += 1
+        ops.lm_head(self.logits, res_a, self.delta, self.ln_f, self.lm_head, s.rms_eps)
+        ops.sample_top_k(self.token, self.out_tokens, self.pos, self.logits, temperature=0.6, top_k=5, seed=self.sample_seed)
 
     # -- driving ----------------------------------------------------------------------------------
     def capture(self):

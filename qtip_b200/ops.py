@@ -294,6 +294,33 @@ def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scal
     return out
 
 
+def embed_token(res, delta, embed, token):
+    """qtip_embed_token: res = embed[token], delta = 0."""
+    _lib.check(_lib.load().qtip_embed_token(res.data_ptr(), delta.data_ptr(), embed.data_ptr(), token.data_ptr(),
+                                            embed.shape[1], _stream()), "qtip_embed_token")
+    global launch_count
+    launch_count += 1
+
+
+def lm_head(logits, res, delta, norm_weight, weight, eps):
+    """qtip_lm_head: logits = weight @ RMSNorm(res + delta) (fp16 norm semantics of LlamaRMSNorm, fp32 logits)."""
+    vocab, hidden = weight.shape
+    _lib.check(_lib.load().qtip_lm_head(logits.data_ptr(), res.data_ptr(), delta.data_ptr(), norm_weight.data_ptr(),
+                                        weight.data_ptr(), hidden, vocab, float(eps), _stream()), "qtip_lm_head")
+    global launch_count
+    launch_count += 1
+    return logits
+
+
+def sample_top_k(token, out_tokens, pos, logits, temperature=0.6, top_k=5, seed=0):
+    """qtip_sample_top_k: next token -> token, out_tokens[pos + 1]; pos += 1 (all on the device)."""
+    _lib.check(_lib.load().qtip_sample_top_k(token.data_ptr(), out_tokens.data_ptr(), pos.data_ptr(), logits.data_ptr(),
+                                             logits.numel(), float(temperature), int(top_k), int(seed), _stream()),
+               "qtip_sample_top_k")
+    global launch_count
+    launch_count += 1
+
+
 def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, theta=10000.0):
     st = _lib.load().qtip_rope_kv_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
                                          pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), _stream())

@@ -219,3 +219,56 @@ def test_attn_decode_matches_fp32_softmax(ctx, heads):
     s = torch.einsum("hd,thd->ht", q.float(), k) / hd ** 0.5
     ref = torch.einsum("ht,thd->hd", torch.softmax(s, dim=-1), v)
     torch.testing.assert_close(out.float(), ref, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(4096, 32000), (512, 1001), (16384, 2048)])
+def test_lm_head_matches_torch(shape):
+    """Final RMSNorm + fp16 head against torch (fp32 accumulation; tolerance 1e-3 relative L2)."""
+    hidden, vocab = shape
+    g = torch.Generator(device="cuda").manual_seed(hidden + vocab)
+    res = torch.randn(hidden, generator=g, device="cuda").half()
+    delta = (0.3 * torch.randn(hidden, generator=g, device="cuda")).half()
+    w_norm = (1 + 0.1 * torch.randn(hidden, generator=g, device="cuda")).half()
+    W = (0.02 * torch.randn(vocab, hidden, generator=g, device="cuda")).half()
+    logits = torch.zeros(vocab, device="cuda")
+    ops.lm_head(logits, res, delta, w_norm, W, 1e-5)
+    h = (res + delta).float()
+    h = (h * torch.rsqrt(h.pow(2).mean() + 1e-5)).half() * w_norm
+    want = h.float() @ W.float().T
+    assert rel_l2(logits.cpu().numpy(), want.cpu().numpy()) < 1e-3
+
+
+@pytest.mark.gpu
+def test_embed_and_sampler():
+    """Embedding lookup is a copy; the sampler returns one of the top-k logits, is reproducible for a seed and a
+    position, follows softmax(top / temperature) over many positions, and advances the position."""
+    vocab, hidden, k = 5000, 256, 5
+    g = torch.Generator(device="cuda").manual_seed(5)
+    embed = torch.randn(vocab, hidden, generator=g, device="cuda").half()
+    tok = torch.tensor([1234], dtype=torch.int64, device="cuda")
+    res = torch.zeros(hidden, dtype=torch.float16, device="cuda")
+    delta = torch.ones(hidden, dtype=torch.float16, device="cuda")
+    ops.embed_token(res, delta, embed, tok)
+    assert torch.equal(res, embed[1234]) and torch.count_nonzero(delta) == 0
+
+    logits = torch.randn(vocab, generator=g, device="cuda")
+    top = torch.topk(logits, k)
+    n_draws = 4000
+    out = torch.full((n_draws + 2,), -1, dtype=torch.int64, device="cuda")
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(n_draws):
+        ops.sample_top_k(tok, out, pos, logits, temperature=0.6, top_k=k, seed=77)
+    torch.cuda.synchronize()
+    assert int(pos) == n_draws and int(out[0]) == -1 and int(tok) == int(out[n_draws])
+    drawn = out[1:n_draws + 1]
+    assert bool(torch.isin(drawn, top.indices).all())
+    want = torch.softmax(top.values / 0.6, dim=0)
+    freq = torch.stack([(drawn == i).float().mean() for i in top.indices])
+    assert torch.allclose(freq, want, atol=0.03)
+    # same seed and positions -> same tokens
+    out2 = torch.full_like(out, -1)
+    pos.zero_()
+    for _ in range(50):
+        ops.sample_top_k(tok, out2, pos, logits, temperature=0.6, top_k=k, seed=77)
+    assert torch.equal(out2[1:51], out[1:51])
