@@ -249,6 +249,15 @@ int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, c
                               void *cache_v, const int *pos, int n_heads, int n_kv_heads, int head_dim, float theta,
                               void *stream);
 
+/* qtip_rope_kv_append_fused and qtip_attn_decode in one launch: from the raw fp32 results of the q / k / v matvecs
+ * to the attention output (n_heads, head_dim) fp16 for one new token at row *pos, appending the rotated k and v
+ * to the caches on the way.  head_dim 128; n_heads and n_kv_heads powers of two (the Walsh-Hadamard transform
+ * over the width factors into one over heads and one inside a head).  Caches 16-byte aligned. */
+int qtip_attn_decode_fused(void *out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
+                           const float *sign_k, const float *sign_v, float scale_q, float scale_kv, void *cache_k,
+                           void *cache_v, const int *pos, int n_heads, int n_kv_heads, int head_dim, float theta,
+                           void *stream);
+
 /* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128;
  * q and the caches 16-byte aligned.
  * Replaces the scaled_dot_product_attention call of LlamaSdpaAttention.forward (model/llama.py:884-891)

@@ -48,6 +48,7 @@ SIGNATURES = {
     "qtip_sample_top_k": (_i, [_vp, _vp, _vp, _vp, _i, _f, _i, ctypes.c_ulonglong, _vp]),
     "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "qtip_attn_decode_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }
 

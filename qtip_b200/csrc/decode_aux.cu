@@ -243,6 +243,209 @@ __global__ void __launch_bounds__(kAttnThreads)
     }
 }
 
+// attn_decode_kernel with everything between the q/k/v matvecs and the attention in front of it, so that a
+// decoder layer needs no separate rotary / cache launch.  The Walsh-Hadamard transform over a width
+// n_heads * 128 factors into one over the head index and one over the 128 values of a head, so the CTA of head h
+// only needs  z[d] = sum_h2 (-1)^popc(h & h2) * y[h2*128 + d]  (a signed sum over heads, every CTA reads all of y)
+// followed by a 128-point transform in one warp.  It does this for its q head and for its k / v head, applies
+// sign * scale, rounds to fp16 like the linear's output tensor, rotates q and k, and the first q head of each
+// k/v group appends k and v to the cache.  Attention then runs over cache rows 0..pos-1 plus the new row, which
+// is taken from shared memory (the cache write of another CTA may not have landed).
+struct AttnFusedArgs {
+    const float *y_q, *y_k, *y_v, *sv_q, *sv_k, *sv_v;
+    float scale_q, scale_kv;
+    __half *out, *cache_k, *cache_v;
+    const int *pos;
+    int n_heads, n_kv;
+    float log2_theta, softmax_scale;
+};
+
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_fused_kernel(const AttnFusedArgs a) {
+    constexpr int hd = 128, G = kAttnGroups, U = kAttnBatch;
+    __shared__ float sc[kAttnChunk + 1];
+    __shared__ float red_max[kAttnThreads / 32], red_sum[kAttnThreads / 32];
+    __shared__ float accs[G][hd + 4];
+    __shared__ float part[3][4][hd];          // signed head sums of q, k, v: four partial sums each
+    __shared__ __align__(16) float cur[3][hd];   // this position's q (rotated, pre-scaled), k (rotated), v
+    const int head = blockIdx.x, rep = a.n_heads / a.n_kv, kvh = head / rep;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, grp = tid >> 4, sub = tid & 15;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int pos = *a.pos;
+
+    // ---- signed sums over heads: thread (quarter, d) adds a quarter of the heads (all three loads batches in flight)
+    {
+        const int d = tid & (hd - 1), quarter = tid >> 7;
+        float s3[3];
+#pragma unroll
+        for (int w = 0; w < 3; w++) {
+            const float *y = w == 0 ? a.y_q : w == 1 ? a.y_k : a.y_v;
+            const int nh = w == 0 ? a.n_heads : a.n_kv, h = w == 0 ? head : kvh;
+            const int per = (nh + 3) >> 2, h0 = quarter * per, h1 = min(nh, h0 + per);
+            float s = 0.f;
+#pragma unroll 8
+            for (int h2 = h0; h2 < h1; h2++) {
+                const float v = __ldcg(y + (size_t)h2 * hd + d);
+                s += (__popc(h & h2) & 1) ? -v : v;
+            }
+            s3[w] = s;
+        }
+#pragma unroll
+        for (int w = 0; w < 3; w++) part[w][quarter][d] = s3[w];
+    }
+    __syncthreads();
+    if (warp < 3) {
+        // warp 0: q, warp 1: k, warp 2: v.  Lane l holds d = l + 32*e, so the rotary partner d + 64 is e + 2.
+        const int w = warp;
+        const float *sv = w == 0 ? a.sv_q : w == 1 ? a.sv_k : a.sv_v;
+        const int h = w == 0 ? head : kvh;
+        const float scale = w == 0 ? a.scale_q : a.scale_kv;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = lane + 32 * e;
+            v[e] = part[w][0][d] + part[w][1][d] + part[w][2][d] + part[w][3][d];
+        }
+        fwht_warp<4>(v, lane);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            v[e] *= scale;
+            if (sv) v[e] *= sv[(size_t)h * hd + lane + 32 * e];
+            v[e] = __half2float(__float2half_rn(v[e]));           // the linear's output is an fp16 tensor
+        }
+        if (w < 2) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int i = lane + 32 * e;
+                const float inv_freq = exp2f(-a.log2_theta * (float)(2 * i) / (float)hd);
+                float sn, cs;
+                sincosf((float)pos * inv_freq, &sn, &cs);
+                const float x0 = v[e], x1 = v[e + 2];
+                v[e] = __half2float(__float2half_rn(x0 * cs - x1 * sn));
+                v[e + 2] = __half2float(__float2half_rn(x1 * cs + x0 * sn));
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = lane + 32 * e;
+            cur[w][d] = w == 0 ? v[e] * a.softmax_scale : v[e];
+            if (w > 0 && head == kvh * rep) {
+                __half *cache = w == 1 ? a.cache_k : a.cache_v;
+                cache[(size_t)pos * a.n_kv * hd + (size_t)kvh * hd + d] = __float2half_rn(v[e]);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- attention over rows 0..pos (row pos from shared memory)
+    const int ctx = pos + 1;
+    const size_t row = (size_t)a.n_kv * hd;
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) qv[i] = cur[0][sub * 8 + i];
+    const __half *kb = a.cache_k + (size_t)kvh * hd + sub * 8, *vb = a.cache_v + (size_t)kvh * hd + sub * 8;
+    auto load_row = [&](const __half *base, const float *fresh, int t_global, float (&f)[8], const uint4 &raw) {
+        if (t_global == pos) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = fresh[sub * 8 + i];
+        } else {
+            unpack8(raw, f);
+        }
+    };
+    float m_run = -INFINITY, d_run = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int c0 = 0; c0 < ctx; c0 += kAttnChunk) {
+        const int cn = min(kAttnChunk, ctx - c0);
+        float lmax = -INFINITY;
+        for (int tb = 0; tb < cn; tb += U * G) {
+            uint4 kr[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                kr[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (t < cn && c0 + t < pos) kr[u] = __ldg(reinterpret_cast<const uint4 *>(kb + (size_t)(c0 + t) * row));
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                float kf[8], s = 0.f;
+                load_row(kb, cur[1], c0 + t, kf, kr[u]);
+#pragma unroll
+                for (int i = 0; i < 8; i++) s = fmaf(qv[i], kf[i], s);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(kFullMask, s, o);
+                if (t < cn) {
+                    if (sub == 0) sc[t] = s;
+                    lmax = fmaxf(lmax, s);
+                }
+            }
+        }
+        uint4 vr[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int t = grp + u * G;
+            vr[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (t < cn && c0 + t < pos) vr[u] = __ldg(reinterpret_cast<const uint4 *>(vb + (size_t)(c0 + t) * row));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
+        if (lane == 0) red_max[warp] = lmax;
+        __syncthreads();
+        float cmax = red_max[0];
+#pragma unroll
+        for (int w = 1; w < kAttnThreads / 32; w++) cmax = fmaxf(cmax, red_max[w]);
+        const float m_new = fmaxf(m_run, cmax);
+        const float corr = __expf(m_run - m_new);
+        float lsum = 0.f;
+        for (int t = tid; t < cn; t += kAttnThreads) {
+            const float pr = __expf(sc[t] - m_new);
+            sc[t] = pr;
+            lsum += pr;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(kFullMask, lsum, o);
+        if (lane == 0) red_sum[warp] = lsum;
+        __syncthreads();
+        float csum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnThreads / 32; w++) csum += red_sum[w];
+        d_run = d_run * corr + csum;
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] *= corr;
+        for (int tb = 0; tb < cn; tb += U * G) {
+            uint4 curv[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) curv[u] = vr[u];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + U * G + grp + u * G;
+                if (t < cn && c0 + t < pos) vr[u] = __ldg(reinterpret_cast<const uint4 *>(vb + (size_t)(c0 + t) * row));
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int t = tb + grp + u * G;
+                if (t < cn) {
+                    float vf[8];
+                    load_row(vb, cur[2], c0 + t, vf, curv[u]);
+                    const float pr = sc[t];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) acc[i] = fmaf(pr, vf[i], acc[i]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) accs[grp][sub * 8 + i] = acc[i];
+    __syncthreads();
+    if (tid < hd) {
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < G; g++) s += accs[g][tid];
+        a.out[(size_t)head * hd + tid] = __float2half_rn(s / d_run);
+    }
+}
+
 template <typename... Args>
 int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -323,4 +526,21 @@ extern "C" int qtip_attn_decode(void *out, const void *q, const void *cache_k, c
     return launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(kAttnThreads), static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(out), static_cast<const __half *>(q), static_cast<const __half *>(cache_k),
                       static_cast<const __half *>(cache_v), pos, n_heads, n_kv_heads, 1.0f / sqrtf((float)head_dim));
+}
+
+extern "C" int qtip_attn_decode_fused(void *out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
+                                      const float *sign_k, const float *sign_v, float scale_q, float scale_kv,
+                                      void *cache_k, void *cache_v, const int *pos, int n_heads, int n_kv_heads,
+                                      int head_dim, float theta, void *stream) {
+    if (!out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+    if (head_dim != 128 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
+    if ((n_heads & (n_heads - 1)) || (n_kv_heads & (n_kv_heads - 1))) return QTIP_ERR_BAD_SHAPE;   // Hadamard over heads
+    if (!aligned(cache_k, 16) || !aligned(cache_v, 16) || !aligned(y_q, 4)) return QTIP_ERR_ALIGNMENT;
+    AttnFusedArgs a = {};
+    a.y_q = y_q; a.y_k = y_k; a.y_v = y_v; a.sv_q = sign_q; a.sv_k = sign_k; a.sv_v = sign_v;
+    a.scale_q = scale_q; a.scale_kv = scale_kv;
+    a.out = static_cast<__half *>(out); a.cache_k = static_cast<__half *>(cache_k); a.cache_v = static_cast<__half *>(cache_v);
+    a.pos = pos; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.log2_theta = log2f(theta);
+    a.softmax_scale = 1.0f / sqrtf((float)head_dim);
+    return launch_pdl(attn_decode_fused_kernel, dim3(n_heads), dim3(kAttnThreads), static_cast<cudaStream_t>(stream), a);
 }

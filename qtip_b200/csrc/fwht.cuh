@@ -184,6 +184,23 @@ __device__ __forceinline__ void storeE_f32(float *p, size_t i, const float (&o)[
     for (int k = 0; k < E; k += 4) *reinterpret_cast<float4 *>(p + i + k) = make_float4(o[k], o[k + 1], o[k + 2], o[k + 3]);
 }
 
+// Walsh-Hadamard transform over the 32*E values of a warp; lane l holds j = l + 32*e
+template <int E>
+__device__ __forceinline__ void fwht_warp(float (&v)[E], int lane) {
+#pragma unroll
+    for (int s = 1; s < E; s <<= 1)
+#pragma unroll
+        for (int k = 0; k < E; k++)
+            if (!(k & s)) { const float a = v[k], b = v[k | s]; v[k] = a + b; v[k | s] = a - b; }
+#pragma unroll
+    for (int bit = 1; bit < 32; bit <<= 1)
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const float o = __shfl_xor_sync(kFullMask, v[k], bit);
+            v[k] = (lane & bit) ? o - v[k] : v[k] + o;
+        }
+}
+
 // Sum over the CTA (scratch: one float per warp).  Contains two barriers.
 __device__ __forceinline__ float block_sum(float x, float *scratch) {
 #pragma unroll

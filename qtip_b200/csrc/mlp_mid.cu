@@ -66,23 +66,6 @@ __device__ __forceinline__ uint32_t pack_h2(__half a, __half b) {
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
 
-// Walsh-Hadamard transform over the 32*E values of a warp; lane l holds j = l + 32*e
-template <int E>
-__device__ __forceinline__ void fwht_warp(float (&v)[E], int lane) {
-#pragma unroll
-    for (int s = 1; s < E; s <<= 1)
-#pragma unroll
-        for (int k = 0; k < E; k++)
-            if (!(k & s)) { const float a = v[k], b = v[k | s]; v[k] = a + b; v[k | s] = a - b; }
-#pragma unroll
-    for (int bit = 1; bit < 32; bit <<= 1)
-#pragma unroll
-        for (int k = 0; k < E; k++) {
-            const float o = __shfl_xor_sync(kFullMask, v[k], bit);
-            v[k] = (lane & bit) ? o - v[k] : v[k] + o;
-        }
-}
-
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_rank() {

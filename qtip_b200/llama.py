@@ -142,6 +142,8 @@ class QtipLlama:
         # NEXT launch (which needs the register transform: 4096 or 8192 wide), that of q/k/v in the rotary kernel
         self.defer_h = tp == 1 and self.fuse_in_h and s.hidden in (4096, 8192)
         self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
+        # ... or, with power-of-two head counts, inside the attention kernel itself (no rotary launch at all)
+        self.attn_fused = self.fuse_in_h and s.head_dim == 128 and pow2(self.n_heads) and pow2(self.n_kv_heads)
         # gate/up output side + SwiGLU + down input side as one cluster launch (widths with a Hadamard factor)
         self.mid_fused = (not self.fuse_out_m) and (not self.fuse_in_m) and ops.mlp_mid_supported(MLP)
         self.mid_table = ops.mlp_mid_table(MLP, dev, self.bits[self.kf_m]) if self.mid_fused else None
@@ -193,8 +195,8 @@ class QtipLlama:
         last = len(self.layers) - 1
         for li, L in enumerate(self.layers):
             # ---- attention block: res_b = res_a + delta ; h = RMSNorm(res_b) ; q,k,v (column-parallel)
-            if self.fuse_in_h and (self.defer_qkv or (self.fuse_out_hl and self.fuse_out_kv)):
-                dq = self.defer_qkv
+            if self.fuse_in_h and (self.attn_fused or self.defer_qkv or (self.fuse_out_hl and self.fuse_out_kv)):
+                dq = self.defer_qkv or self.attn_fused
                 fin = dict(delta_src, residual=res_a, residual_out=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32)
                 if H == KV:
                     self._linears([L["q"], L["k"], L["v"]], None, [y_q, y_k, y_v], s.hidden, H,
@@ -222,15 +224,20 @@ class QtipLlama:
                     sv = L["SV_kv"] = torch.cat([L["k"].SV32, L["v"].SV32]).contiguous()
                 ops.rht_fused(self.y_qkv[H:], 2, KV, self.qkv[H:], sign_out=sv, hadk_bits=bits[self.kf_kv],
                               kfac=self.kf_kv, scale=inv_kv)
-            if dq:
+            if dq and self.attn_fused:
+                ops.attn_decode_fused(self.attn, y_q, y_k, y_v, L["q"].SV32, L["k"].SV32, L["v"].SV32, inv_hl, inv_kv,
+                                      self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                                      s.head_dim, s.rope_theta)
+            elif dq:
                 ops.rope_kv_append_fused(q, y_q, y_k, y_v, L["q"].SV32, L["k"].SV32, L["v"].SV32, inv_hl, inv_kv,
                                          self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
                                          s.head_dim, s.rope_theta)
             else:
                 ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
                                    s.head_dim, s.rope_theta)
-            ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                            s.head_dim)
+            if not (dq and self.attn_fused):
+                ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
+                                s.head_dim)
             # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
             defer = self.defer_h
             fuse_out = tp1 and self.fuse_out_h and not defer

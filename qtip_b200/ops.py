@@ -342,6 +342,20 @@ def rope_kv_append_fused(q_out, y_q, y_k, y_v, sign_q, sign_k, sign_v, scale_q, 
     launch_count += 1
 
 
+def attn_decode_fused(out, y_q, y_k, y_v, sign_q, sign_k, sign_v, scale_q, scale_kv, cache_k, cache_v, pos, n_heads,
+                      n_kv_heads, head_dim, theta=10000.0):
+    """qtip_attn_decode_fused: output side of q/k/v + rotary + cache append + single-query attention, one launch."""
+    ptr = lambda t: 0 if t is None else t.data_ptr()   # noqa: E731
+    st = _lib.load().qtip_attn_decode_fused(out.data_ptr(), y_q.data_ptr(), y_k.data_ptr(), y_v.data_ptr(), ptr(sign_q),
+                                            ptr(sign_k), ptr(sign_v), float(scale_q), float(scale_kv), cache_k.data_ptr(),
+                                            cache_v.data_ptr(), pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta),
+                                            _stream())
+    _lib.check(st, "qtip_attn_decode_fused")
+    global launch_count
+    launch_count += 1
+    return out
+
+
 def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
     st = _lib.load().qtip_attn_decode(out.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(),
                                       n_heads, n_kv_heads, head_dim, _stream())

@@ -329,6 +329,39 @@ def test_mlp_mid_matches_two_rht_launches(n):
         assert rel_l2(out.float().cpu().numpy(), want.float().cpu().numpy()) < 2e-3
 
 
+@pytest.mark.parametrize("heads", [(32, 32), (32, 8), (4, 4), (8, 1)])
+@pytest.mark.parametrize("pos_v", [0, 1, 37, 300])
+def test_attn_decode_fused_matches_separate_launches(heads, pos_v):
+    """qtip_attn_decode_fused == output-side RHT of q/k/v + rotary / cache append + attention."""
+    import math
+    n_heads, n_kv = heads
+    hd, maxpos = 128, 304
+    H, KV = n_heads * hd, n_kv * hd
+    g = torch.Generator().manual_seed(n_heads * 1000 + n_kv * 10 + pos_v)
+    y = [torch.randn(w, generator=g).to(DEV) for w in (H, KV, KV)]
+    sv = [(torch.randn(w, generator=g).sign() * 0.5).to(DEV) for w in (H, KV, KV)]
+    pos = torch.tensor([pos_v], dtype=torch.int32, device=DEV)
+    ck = (0.5 * torch.randn(maxpos, KV, generator=g)).half().to(DEV)
+    cv = (0.5 * torch.randn(maxpos, KV, generator=g)).half().to(DEV)
+    ck2, cv2 = ck.clone(), cv.clone()
+    q, k, v = [ops.rht(t.view(1, -1), sign_out=s_, scale=1 / math.sqrt(t.numel()), out_dtype=torch.float16).view(-1)
+               for t, s_ in zip(y, sv)]
+    ops.rope_kv_append(q, k, v, ck, cv, pos, n_heads, n_kv, hd, 10000.0)
+    want = torch.zeros(n_heads, hd, dtype=torch.float16, device=DEV)
+    ops.attn_decode(want, q, ck, cv, pos, n_heads, n_kv, hd)
+    got = torch.zeros(n_heads, hd, dtype=torch.float16, device=DEV)
+    ops.attn_decode_fused(got, y[0], y[1], y[2], sv[0], sv[1], sv[2], 1 / math.sqrt(H), 1 / math.sqrt(KV), ck2, cv2, pos,
+                          n_heads, n_kv, hd, 10000.0)
+    torch.cuda.synchronize()
+    assert rel_l2(got.float().cpu().numpy(), want.float().cpu().numpy()) < 2e-3
+    # the cache rows: the new one equal up to fp16 rounding of the transform, every other untouched
+    assert rel_l2(ck2[pos_v].float().cpu().numpy(), ck[pos_v].float().cpu().numpy()) < 1e-3
+    assert rel_l2(cv2[pos_v].float().cpu().numpy(), cv[pos_v].float().cpu().numpy()) < 1e-3
+    keep = torch.ones(maxpos, dtype=torch.bool, device=DEV)
+    keep[pos_v] = False
+    assert torch.equal(ck2[keep], ck[keep]) and torch.equal(cv2[keep], cv[keep])
+
+
 def test_quip_lib_op_under_graph_capture():
     """The torch op boundary (lib/codebook/__init__.py:68-93 upstream): eager call and CUDA-graph replay."""
     from qtip_b200 import codebook_ops
