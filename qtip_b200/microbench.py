@@ -2,6 +2,8 @@
 
     python -m qtip_b200.microbench                       # Llama-2-7B shapes, K = 2, 3, 4, batch 1
     python -m qtip_b200.microbench --shapes 8192x8192,28672x8192 --bits 2 --batch 1,4,8
+    python -m qtip_b200.microbench --shapes 8192x8192 --bits 2 --batch 16,64         # tcgen05 decompress-GEMM
+    python -m qtip_b200.microbench --mlp-mid 11008 --rht 11008                        # transform kernels
     python -m qtip_b200.microbench --shapes 4096x11008 --bits 2 --plain-launches 8   # for a profiler
 
 Timing method (the one of qtip-kernels/test_decompress_matvec.py:69-91 upstream, scaled up): the
@@ -26,7 +28,9 @@ def _sets(m, n, K, bs, code, device, min_bytes=400e6, max_sets=48):
 
 
 def _launch(lay, code, K, m, n, out, ws):
-    if code == "hyb":
+    if code == "hyb" and lay["x"].shape[0] > ops.MAX_MATVEC_BATCH:
+        ops.decompress_gemm(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out)      # tcgen05 path, batches 9..64
+    elif code == "hyb":
         ops.decompress_matvec(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out, workspace=ws)
     else:
         ops.decompress_matvec_plain(lay["codes"], lay["x"], code, K, m, n, out=out, workspace=ws)
@@ -34,7 +38,7 @@ def _launch(lay, code, K, m, n, out, ws):
 
 def time_matvec(m, n, K, bs=1, code="hyb", device="cuda:0", replays=20):
     lays = _sets(m, n, K, bs, code, device)
-    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, bs), dtype=torch.uint8, device=device)
+    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, min(bs, ops.MAX_MATVEC_BATCH)), dtype=torch.uint8, device=device)
     out = torch.empty(bs, m, device=device)
     stream = torch.cuda.Stream(device=device)
     stream.wait_stream(torch.cuda.current_stream(device))
@@ -63,7 +67,7 @@ def time_matvec(m, n, K, bs=1, code="hyb", device="cuda:0", replays=20):
 def plain_launches(m, n, K, bs, code, count, device="cuda:0"):
     """`count` ordinary stream launches over rotating weight sets (what a profiler should capture)."""
     lays = _sets(m, n, K, bs, code, device, min_bytes=160e6, max_sets=14)
-    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, bs), dtype=torch.uint8, device=device)
+    ws = torch.zeros(_lib.load().qtip_matvec_workspace_bytes(m, n, min(bs, ops.MAX_MATVEC_BATCH)), dtype=torch.uint8, device=device)
     out = torch.empty(bs, m, device=device)
     for i in range(count):
         _launch(lays[i % len(lays)], code, K, m, n, out, ws)
@@ -138,7 +142,8 @@ def main():
             us = time_rht(n, plain=args.plain_launches, mid=True)
             if us is not None:
                 print(f"mlp_mid n={n} (factor {ops.had_factor(n)}): {us:7.2f} us per launch (back-to-back launches in one graph)", flush=True)
-        return
+        if not args.rht:
+            return
     if args.rht:
         for n in (int(v) for v in args.rht.split(",")):
             us = time_rht(n, plain=args.plain_launches)
