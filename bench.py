@@ -249,6 +249,8 @@ def run_gpu(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
 
+    if model.peers is not None and int(model.peers.status) != 0:
+        raise RuntimeError("a wait for a peer GPU's flag ran out during the run: the numbers are invalid")
     out = None
     if rank == 0:
         us, byts, launches = measure_matvec_roofline(model, torch)

@@ -103,6 +103,13 @@ int qtip_decompress_gemm(float *out, const void *codes, const void *x, const voi
  *   output side (out != NULL; needs m a power of two <= 16384): the CTA that finishes last computes
  *       out = sign_out * H_m(y) * out_scale  (fp16 or fp32).
  * H is the unnormalised Walsh-Hadamard transform; fold n^-1/2, /32 and x32 into the scales as for qtip_rht.
+ *   tensor parallelism: a row-parallel linear leaves a partial y on every GPU.  Instead of an all-reduce launch
+ *       between it and its consumer, the producer launch (signal_count > 0) also stores every value of y, stamped
+ *       with a sequence number in the same 8-byte store, into a vector on every GPU (peer-mapped memory), and the
+ *       consumer launch (peer_count > 0, n = 4096 or 8192) re-reads those vectors in its own memory until each
+ *       value carries the expected stamp, adds the vectors in rank order and continues as for in_y.  No fence,
+ *       flag or atomic lies between the GPUs.  Vectors may be reused every second producer/consumer pair (the
+ *       protocol of qtip_b200/tp.py alternates two).  The wait is bounded; peer_status reports a time-out.
  * Either all descriptors of a call use the fused input side or none does.  Every descriptor needs its
  * own zero-initialised workspace (qtip_matvec_workspace_bytes) and its own y. */
 typedef struct qtip_linear_desc {
@@ -127,6 +134,15 @@ typedef struct qtip_linear_desc {
     const float *in_y;            /* (n) fp32 raw output of the producer linear, or NULL */
     const float *in_y_sign;       /* (n) fp32, the producer's sign_out; or NULL */
     float in_y_scale;             /* the producer's out_scale */
+    /* tensor parallelism without an all-reduce launch (see above); all zero / NULL when unused */
+    int peer_count;               /* consumer: number of GPUs whose partial vectors are summed instead of in_y */
+    const void *peer_y[8];        /* GPU p's stamped vector ((n) pairs {fp32 value, uint32 stamp}) in THIS GPU's memory */
+    const unsigned *peer_seq;     /* this GPU's sequence counter (the one its own producer launch advances) */
+    unsigned *peer_status;        /* set to non-zero if a wait ran out */
+    unsigned peer_max_polls;      /* bound on the re-reads of one element group (0: 1 Mi) */
+    int signal_count;             /* producer: number of GPUs that receive the result */
+    void *signal_y[8];            /* GPU p's stamped vector for THIS rank (peer-mapped; this GPU's own included) */
+    unsigned *signal_seq;         /* this GPU's sequence counter, advanced by one per launch */
 } qtip_linear_desc;
 int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream);
 

@@ -20,7 +20,9 @@ class LinearDesc(ctypes.Structure):
     _fields_ = [("y", _vp), ("codes", _vp), ("tlut", _vp), ("x", _vp), ("workspace", _vp), ("workspace_bytes", _sz),
                 ("in_raw", _vp), ("residual", _vp), ("residual_out", _vp), ("norm_weight", _vp), ("gate", _vp),
                 ("sign_in", _vp), ("in_scale", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("sign_out", _vp),
-                ("out_scale", _f), ("in_y", _vp), ("in_y_sign", _vp), ("in_y_scale", _f)]
+                ("out_scale", _f), ("in_y", _vp), ("in_y_sign", _vp), ("in_y_scale", _f),
+                ("peer_count", _i), ("peer_y", _vp * 8), ("peer_seq", _vp), ("peer_status", _vp),
+                ("peer_max_polls", ctypes.c_uint), ("signal_count", _i), ("signal_y", _vp * 8), ("signal_seq", _vp)]
 
 
 # name -> (restype, argtypes); mirrors include/qtip_b200.h

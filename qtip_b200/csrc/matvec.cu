@@ -129,6 +129,17 @@ struct SegmentIter {
     }
 };
 
+// Extra destinations of a result row block (tensor parallelism): this rank's slot in every GPU's peer-mapped
+// buffer.  Each value travels as one 8-byte store {value, stamp}; the reader knows a value has arrived when its
+// stamp is the expected sequence number, so no fence, flag or atomic sits between producer and consumers.
+struct OutCopies {
+    uint2 *dst[8];
+    int n;
+};
+__device__ __forceinline__ void store_stamped(uint2 *p, float v, unsigned stamp) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
+}
+
 struct Shared {            // control block at the start of dynamic shared memory
     int is_last;
     int pad_[7];
@@ -145,7 +156,7 @@ template <int NW>
 __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, Shared *sh, float *__restrict__ out,
                                                float *__restrict__ partial, unsigned *__restrict__ counters, long M,
                                                long nb, long B, long G, int kmax, int m, int bs, bool whole_row,
-                                               bool trailing_sync = true) {
+                                               bool trailing_sync, const OutCopies &copies, unsigned stamp) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int stride = 32 * bs;
@@ -171,7 +182,10 @@ __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, S
         contributors = (int)(cta_of_block((M + 1) * nb - 1, B, G) - c_first) + 1;
     }
     if (contributors == 1) {
-        if (tid < stride) out[(size_t)b * m + 32 * M + r] = v;
+        if (tid < stride) {
+            out[(size_t)b * m + 32 * M + r] = v;
+            for (int q = 0; q < copies.n; q++) store_stamped(copies.dst[q] + (size_t)b * m + 32 * M + r, v, stamp);
+        }
         if (trailing_sync) asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
         return;
     }
@@ -191,6 +205,7 @@ __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, S
             float s = 0.f;
             for (int c = 0; c < contributors; c++) s += __ldcg(slot + (size_t)c * 256 + tid);
             out[(size_t)b * m + 32 * M + r] = s;
+            for (int q = 0; q < copies.n; q++) store_stamped(copies.dst[q] + (size_t)b * m + 32 * M + r, s, stamp);
         }
         if (tid == 0) counters[M] = 0;  // leave the workspace ready for the next call
     }
@@ -275,6 +290,25 @@ struct FusedOut {   // final != nullptr: final = sign_out * H(out) * scale, comp
     float scale;
     int dtype;
 };
+// Tensor parallelism without a separate all-reduce launch.  A row-parallel linear leaves a PARTIAL y on every
+// GPU; the consumer's deferred output side (FusedIn::y_prev) then has to start from the sum over GPUs.
+// Signal (producer): every result value is also stored, stamped with the sequence number *seq + 1, into this
+// rank's vector on every GPU (copies); the CTA that finishes last then advances *seq.
+// PeerIn (consumer): y[p] is GPU p's stamped vector in THIS GPU's memory; a thread re-reads its elements until
+// they carry the stamp *seq (its own GPU's producer launch has already advanced it), at most max_polls times -
+// then it sets *status and goes on (wrong numbers, but the kernel terminates).
+constexpr int kMaxPeers = 8;
+struct PeerIn {
+    const uint2 *y[kMaxPeers];
+    const unsigned *seq;
+    unsigned *status;
+    unsigned max_polls;
+    int n;
+};
+struct Signal {
+    unsigned *seq;
+    OutCopies copies;
+};
 struct MatvecProblem {
     float *out;
     const uint8_t *codes;
@@ -283,6 +317,8 @@ struct MatvecProblem {
     uint8_t *workspace;
     FusedIn in;
     FusedOut ep;
+    PeerIn peer;
+    Signal sig;
 };
 constexpr int kMaxProblems = 4;
 struct MatvecBatch {
@@ -298,20 +334,68 @@ __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, i
     return o;
 }
 
+// E consecutive stamped values of one GPU's partial vector: re-read until every stamp is `want` (bounded)
+template <int E>
+__device__ __forceinline__ bool loadE_stamped(const uint2 *p, size_t i, unsigned want, unsigned max_polls, float (&o)[E]) {
+    for (unsigned polls = 0;; polls++) {
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < E; k += 2) {
+            uint4 q;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p + i + k) : "memory");
+            o[k] = __uint_as_float(q.x); o[k + 1] = __uint_as_float(q.z);
+            ok = ok && q.y == want && q.w == want;
+        }
+        if (ok) return true;
+        if (polls >= max_polls) return false;
+        __nanosleep(1000);
+    }
+}
+
+// Before the whole CTA reads the vectors, one warp watches 32 sample elements of each until they are current:
+// the other 31 warps stay off the memory system while the data is still on its way (150 000 threads re-reading
+// with system scope slow the arriving stores down by orders of magnitude).  Bounded like the reads themselves.
+__device__ __forceinline__ void await_samples(const PeerIn &peer, int n, unsigned want) {
+    if (threadIdx.x < 32) {
+        const size_t idx = (size_t)threadIdx.x * (n >> 5);
+        for (int p = 0; p < peer.n; p++) {
+            for (unsigned polls = 0; polls < peer.max_polls; polls++) {
+                uint2 q;
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(peer.y[p] + idx) : "memory");
+                if (__all_sync(kFullMask, q.y == want)) break;
+                __nanosleep(200);
+            }
+        }
+    }
+    __syncthreads();
+}
+
 // Fused input side for n = 1024*E (E = 4, 8, 16): a thread owns E consecutive values, everything up to the
 // Walsh-Hadamard transform stays in registers (see fwht_regs), the result goes to xs in fragment order.
 template <int E>
-__device__ __forceinline__ void fused_input_regs(const FusedIn &I, int n, uint4 *xs, float *buf, float *warp_sums) {
+__device__ __forceinline__ void fused_input_regs(const FusedIn &I, const PeerIn &peer, int n, uint4 *xs, float *buf, float *warp_sums) {
     // ownership of the E consecutive values a thread works on: tid*E ("A"), or, after one fwht_regs,
     // (lane*32 + warp)*E ("B").  The transform maps A to B and B to A, every other step is element-wise or
     // a sum over everything, so the deferred-producer path simply does its element-wise work in B.
-    const bool deferred = I.y_prev != nullptr;
+    const bool deferred = I.y_prev != nullptr || peer.n > 0;
     const size_t jA = (size_t)threadIdx.x * E;
     const size_t jB = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
     const size_t j = deferred ? jB : jA;
     float v[E], rs[E], wn[E], gt[E], sg[E];
     // all operand vectors are requested before any is used
-    if (deferred) loadE_f32<E>(I.y_prev, jA, v, true);
+    if (peer.n > 0) {
+        const unsigned want = *reinterpret_cast<const volatile unsigned *>(peer.seq);
+        await_samples(peer, n, want);
+        bool ok = loadE_stamped<E>(peer.y[0], jA, want, peer.max_polls, v);
+        for (int p = 1; p < peer.n; p++) {      // same order on every GPU: the sums are bit-identical
+            float t[E];
+            ok = loadE_stamped<E>(peer.y[p], jA, want, peer.max_polls, t) && ok;
+#pragma unroll
+            for (int k = 0; k < E; k++) v[k] += t[k];
+        }
+        if (!ok) atomicOr(peer.status, 1u);
+    } else if (deferred) loadE_f32<E>(I.y_prev, jA, v, true);
     else loadE_f16<E>(I.x_raw, j, v);
     if (I.residual) loadE_f16<E>(I.residual, j, rs);
     if (I.norm_weight) loadE_f16<E>(I.norm_weight, j, wn);
@@ -440,15 +524,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
+    // tensor parallelism: the stamp of this launch's result values (every CTA reads the counter before any CTA can
+    // have taken its exit ticket, and only the last ticket holder advances it)
+    const unsigned stamp = P.sig.seq ? *reinterpret_cast<const volatile unsigned *>(P.sig.seq) + 1u : 0u;
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
-        if (P.in.x_raw || P.in.y_prev) {
+        if (P.in.x_raw || P.in.y_prev || P.peer.n > 0) {
             // fused input side (bs == 1, n a power of two): every CTA transforms the activation itself.
             // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
             // the whole prologue costs one L2 round trip, not one per array.
             const FusedIn &I = P.in;
-            if (n == 4096) fused_input_regs<4>(I, n, xs, fscratch, sh->warp_sums);
-            else if (n == 8192) fused_input_regs<8>(I, n, xs, fscratch, sh->warp_sums);
+            if (n == 4096) fused_input_regs<4>(I, P.peer, n, xs, fscratch, sh->warp_sums);
+            else if (n == 8192) fused_input_regs<8>(I, P.peer, n, xs, fscratch, sh->warp_sums);
             else {
             const int nvec = n >> 3;
             float ss = 0.f;
@@ -577,13 +664,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
         finish_segment<kConsumerWarps>(acc, DB ? red + (segno & 1) * red_floats : red, sh, out, partial, counters, M, nb,
-                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB);
+                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB, P.sig.copies, stamp);
         segno++;
         pos = npos;
         seg_end = nseg_end;
     }
 
-    if (P.ep.final) {
+    if (P.sig.seq) {
+        // row-parallel partial result: the values are already on their way to every GPU (stamped); the CTA that
+        // finishes last advances the sequence counter that the stamps of the next launch are derived from
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+                *P.sig.seq = stamp;
+                *done_counter = 0;
+            }
+        }
+    } else if (P.ep.final) {
         // fused output side (m a power of two): the CTA that finishes last transforms the whole result
         __threadfence();
         __syncthreads();
@@ -709,7 +806,8 @@ __global__ void __launch_bounds__(kPlainWarps * 32, 2)
                 mma_16816(acc[ms], a, b0, b1);
             }
         }
-        finish_segment<kPlainWarps>(acc, red, sh, out, partial, counters, M, nb, B, G, kmax, m, bs, mode == kModeRows);
+        finish_segment<kPlainWarps>(acc, red, sh, out, partial, counters, M, nb, B, G, kmax, m, bs, mode == kModeRows, true,
+                                    OutCopies{}, 0u);
     }
 }
 
@@ -839,10 +937,10 @@ extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K
     for (int i = 0; i < count; i++) {
         const qtip_linear_desc &d = descs[i];
         if (!d.tlut) return QTIP_ERR_BAD_ARG;
-        const bool fin = d.in_raw != nullptr || d.in_y != nullptr, fout = d.out != nullptr;
+        const bool fin = d.in_raw != nullptr || d.in_y != nullptr || d.peer_count > 0, fout = d.out != nullptr;
         if (i > 0 && fin != fused_in) return QTIP_ERR_BAD_ARG;   // all or none: the shared-memory layout is per launch
         fused_in = fin;
-        const void *x = d.in_y ? (const void *)d.in_y : fin ? d.in_raw : d.x;
+        const void *x = d.peer_count > 0 ? d.peer_y[0] : d.in_y ? (const void *)d.in_y : fin ? d.in_raw : d.x;
         int st = check_common(d.y, d.codes, x, K, m, n, bs, d.workspace, d.workspace_bytes);
         if (st != QTIP_OK) return st;
         if (!aligned(d.tlut, 4)) return QTIP_ERR_ALIGNMENT;
@@ -871,6 +969,25 @@ extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K
             P.in.y_prev = d.in_y; P.in.prev_sign = d.in_y_sign; P.in.prev_scale = d.in_y_scale;
         }
         if (fout) { P.ep.final = d.out; P.ep.sign_out = d.sign_out; P.ep.scale = d.out_scale; P.ep.dtype = d.out_dtype; }
+        if (d.peer_count > 0) {
+            if (d.peer_count > kMaxPeers || !d.peer_seq || !d.peer_status || !fin) return QTIP_ERR_BAD_ARG;
+            if (n != 4096 && n != 8192) return QTIP_ERR_BAD_SHAPE;
+            for (int q = 0; q < d.peer_count; q++) {
+                if (!d.peer_y[q] || !aligned(d.peer_y[q], 16)) return QTIP_ERR_BAD_ARG;
+                P.peer.y[q] = static_cast<const uint2 *>(d.peer_y[q]);
+            }
+            P.peer.n = d.peer_count; P.peer.seq = d.peer_seq; P.peer.status = d.peer_status;
+            P.peer.max_polls = d.peer_max_polls ? d.peer_max_polls : (1u << 20);
+            P.in.prev_sign = d.in_y_sign; P.in.prev_scale = d.in_y_scale;
+        }
+        if (d.signal_count > 0) {
+            if (d.signal_count > kMaxPeers || !d.signal_seq || fout) return QTIP_ERR_BAD_ARG;
+            for (int q = 0; q < d.signal_count; q++) {
+                if (!d.signal_y[q] || !aligned(d.signal_y[q], 16)) return QTIP_ERR_BAD_ARG;
+                P.sig.copies.dst[q] = static_cast<uint2 *>(d.signal_y[q]);
+            }
+            P.sig.copies.n = d.signal_count; P.sig.seq = d.signal_seq;
+        }
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (K == 2) return launch_hyb_batch<2>(batch, count, m, n, bs, fused_in, s);

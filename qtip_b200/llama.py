@@ -19,6 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from . import ops
+from . import tp as tp_mod
 
 
 @dataclass
@@ -140,13 +141,22 @@ class QtipLlama:
         self.fuse_out_h, self.fuse_out_hl, self.fuse_out_kv, self.fuse_out_m = fout(s.hidden), fout(H), fout(KV), fout(MLP)
         # deferred output sides: the Hadamard transform + sign of o_proj / down_proj runs in the prologue of the
         # NEXT launch (which needs the register transform: 4096 or 8192 wide), that of q/k/v in the rotary kernel
-        self.defer_h = tp == 1 and self.fuse_in_h and s.hidden in (4096, 8192)
+        self.defer_h = self.fuse_in_h and s.hidden in (4096, 8192)
+        # tp > 1: the partial results of o_proj / down_proj stay where they are; the next launch on every GPU waits
+        # for all GPUs' flags and adds the partial vectors through peer-mapped memory (no all-reduce launch)
+        self.peers = None
+        if tp > 1 and self.defer_h:
+            self.peers = tp_mod.PeerBuffers(s.hidden, tp_rank, tp_size, group, dev)
         self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
         # ... or, with power-of-two head counts, inside the attention kernel itself (no rotary launch at all)
         self.attn_fused = self.fuse_in_h and s.head_dim == 128 and pow2(self.n_heads) and pow2(self.n_kv_heads)
         # gate/up output side + SwiGLU + down input side as one cluster launch (widths with a Hadamard factor)
         self.mid_fused = (not self.fuse_out_m) and (not self.fuse_in_m) and ops.mlp_mid_supported(MLP)
         self.mid_table = ops.mlp_mid_table(MLP, dev, self.bits[self.kf_m]) if self.mid_fused else None
+        if self.peers is not None:
+            import torch.distributed as dist
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=group)           # start the flag protocol with every rank ready
         self.graph = None
         self.n_launches_per_step = None   # counted while the step runs (library launches only)
 
@@ -159,7 +169,7 @@ class QtipLlama:
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 
-    def _linears(self, lins, xs_or_raw, ys, n, m, *, fused_in=None, outs=None, sign_outs=None, out_scale=1.0):
+    def _linears(self, lins, xs_or_raw, ys, n, m, *, fused_in=None, outs=None, sign_outs=None, out_scale=1.0, extra=None):
         """One launch for the same-shape linears `lins`.  fused_in: dict(in_raw, residual, residual_out, norm_weight,
         gate, sign_ins, in_scale) or None (then xs_or_raw holds the transformed fp16 inputs).  outs: fused output side."""
         descs = []
@@ -177,6 +187,10 @@ class QtipLlama:
                     d["residual_out"] = fused_in.get("residual_out")
             if outs is not None:
                 d.update(out=outs[i], sign_out=sign_outs[i], out_scale=out_scale)
+            if fused_in is not None and "peer" in fused_in:
+                d.update(fused_in["peer"])
+            if extra:
+                d.update(extra)
             descs.append(d)
         ops.linear_fused(descs, lins[0].K, m, n, 1)
 
@@ -240,17 +254,23 @@ class QtipLlama:
                                 s.head_dim)
             # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
             defer = self.defer_h
+            use_peers = defer and self.peers is not None
             fuse_out = tp1 and self.fuse_out_h and not defer
+            y_o = self.y_h
+            sig = self.peers.signal(0) if use_peers else None
             if self.fuse_in_hl:
-                self._linears([L["o"]], None, [self.y_h], H, s.hidden,
+                self._linears([L["o"]], None, [y_o], H, s.hidden,
                               fused_in=dict(in_raw=self.attn, sign_ins=[L["o"].SU], in_scale=inv_hl / 32),
-                              outs=[self.delta] if fuse_out else None, sign_outs=[L["o"].SV32], out_scale=inv_h)
+                              outs=[self.delta] if fuse_out else None, sign_outs=[L["o"].SV32], out_scale=inv_h, extra=sig)
             else:
                 ops.rht_fused(self.attn, 1, H, self.xh_o, sign_in=L["o"].SU, hadk_bits=bits[self.kf_hl], kfac=self.kf_hl,
                               transpose=True, scale=inv_hl / 32)
-                self._linears([L["o"]], [self.xh_o], [self.y_h], H, s.hidden, outs=[self.delta] if fuse_out else None,
-                              sign_outs=[L["o"].SV32], out_scale=inv_h)
-            if defer:
+                self._linears([L["o"]], [self.xh_o], [y_o], H, s.hidden, outs=[self.delta] if fuse_out else None,
+                              sign_outs=[L["o"].SV32], out_scale=inv_h, extra=sig)
+            if use_peers:
+                delta_src = dict(peer=self.peers.consume(0), in_y_sign=L["o"].SV32, in_y_scale=inv_h)
+            elif defer:
+                self._all_reduce(self.y_h)
                 delta_src = dict(in_y=self.y_h, in_y_sign=L["o"].SV32, in_y_scale=inv_h)
             else:
                 delta_src = dict(in_raw=self.delta)
@@ -284,19 +304,25 @@ class QtipLlama:
                               kfac=self.kf_m, scale=inv_m)
             # ---- down_proj (row-parallel), input silu(gate) * up
             defer = self.defer_h and li != last       # the last layer's result is read by the final norm
+            use_peers = defer and self.peers is not None
             fuse_out = tp1 and self.fuse_out_h and not defer
+            y_d = self.y_h
+            sig = self.peers.signal(1) if use_peers else None
             if self.fuse_in_m:
-                self._linears([L["down"]], None, [self.y_h], MLP, s.hidden,
+                self._linears([L["down"]], None, [y_d], MLP, s.hidden,
                               fused_in=dict(in_raw=self.gu[MLP:], gate=self.gu[:MLP], sign_ins=[L["down"].SU], in_scale=inv_m / 32),
-                              outs=[self.delta] if fuse_out else None, sign_outs=[L["down"].SV32], out_scale=inv_h)
+                              outs=[self.delta] if fuse_out else None, sign_outs=[L["down"].SV32], out_scale=inv_h, extra=sig)
             else:
                 xd = self.xh_d
                 if not mid:
                     ops.rht_fused(self.gu[MLP:], 1, MLP, xd, gate=self.gu[:MLP], sign_in=L["down"].SU,
                                   hadk_bits=bits[self.kf_m], kfac=self.kf_m, transpose=True, scale=inv_m / 32)
-                self._linears([L["down"]], [xd], [self.y_h], MLP, s.hidden, outs=[self.delta] if fuse_out else None,
-                              sign_outs=[L["down"].SV32], out_scale=inv_h)
-            if defer:
+                self._linears([L["down"]], [xd], [y_d], MLP, s.hidden, outs=[self.delta] if fuse_out else None,
+                              sign_outs=[L["down"].SV32], out_scale=inv_h, extra=sig)
+            if use_peers:
+                delta_src = dict(peer=self.peers.consume(1), in_y_sign=L["down"].SV32, in_y_scale=inv_h)
+            elif defer:
+                self._all_reduce(self.y_h)
                 delta_src = dict(in_y=self.y_h, in_y_sign=L["down"].SV32, in_y_scale=inv_h)
             else:
                 delta_src = dict(in_raw=self.delta)

@@ -369,7 +369,9 @@ def linear_fused(descs, K, m, n, bs=1):
     """qtip_linear_fused: one launch for up to four same-shape linears, transforms optionally fused.
     `descs` is a list of dicts with tensor values for the fields of qtip_linear_desc (missing = NULL):
     y, codes, tlut, x, workspace, in_raw, residual, residual_out, norm_weight, gate, sign_in, out, sign_out, in_y,
-    in_y_sign plus floats in_scale, eps, out_scale, in_y_scale."""
+    in_y_sign plus floats in_scale, eps, out_scale, in_y_scale; for tensor parallelism without an all-reduce launch
+    also peer_y / signal_y (lists of device addresses), peer_seq, peer_status, signal_seq (addresses)
+    and peer_max_polls."""
     arr = (_lib.LinearDesc * len(descs))()
     for d, c in zip(descs, arr):
         for name in ("y", "codes", "tlut", "x", "workspace", "in_raw", "residual", "residual_out", "norm_weight", "gate",
@@ -379,6 +381,18 @@ def linear_fused(descs, K, m, n, bs=1):
         c.workspace_bytes = d["workspace"].numel()
         c.in_scale, c.eps, c.out_scale = float(d.get("in_scale", 1.0)), float(d.get("eps", 0.0)), float(d.get("out_scale", 1.0))
         c.in_y_scale = float(d.get("in_y_scale", 1.0))
+        # raw device addresses (ints): peer-mapped memory has no tensor on this side
+        peers = d.get("peer_y") or []
+        c.peer_count = len(peers)
+        for q, ptr in enumerate(peers):
+            c.peer_y[q] = int(ptr)
+        for name in ("peer_seq", "peer_status", "signal_seq"):
+            setattr(c, name, int(d[name]) if d.get(name) else None)
+        c.peer_max_polls = int(d.get("peer_max_polls", 0))
+        sig = d.get("signal_y") or []
+        c.signal_count = len(sig)
+        for q, ptr in enumerate(sig):
+            c.signal_y[q] = int(ptr)
         c.out_dtype = F16 if d.get("out") is None else _dtype_id(d["out"])
     st = _lib.load().qtip_linear_fused(arr, len(descs), K, m, n, bs, _stream())
     _lib.check(st, "qtip_linear_fused")

@@ -362,6 +362,65 @@ def test_attn_decode_fused_matches_separate_launches(heads, pos_v):
     assert torch.equal(ck2[keep], ck[keep]) and torch.equal(cv2[keep], cv[keep])
 
 
+def test_linear_fused_peer_sum_and_signal():
+    """Tensor parallelism without an all-reduce launch, emulated on one GPU: the producer stores its result as
+    stamped values and advances the sequence counter; the consumer adds two stamped vectors once their stamps are
+    current; a vector that nobody refreshes makes the (bounded) wait give up with a status instead of hanging."""
+    import math
+    from qtip_b200 import _lib
+    K, m, n = 2, 4096, 4096
+    lay = synth.make_layer(m, n, K, seed=4242)
+    g = torch.Generator().manual_seed(11)
+    codes, tl = t16(lay["codes"]), torch.from_numpy(lay["tlut"]).to(DEV)
+    need = _lib.load().qtip_matvec_workspace_bytes(m, n, 1)
+    ws = lambda: torch.zeros(need, dtype=torch.uint8, device=DEV)   # noqa: E731
+
+    def stamped(vec, stamp):
+        pairs = torch.empty(vec.numel(), 2, dtype=torch.int32, device=DEV)
+        pairs[:, 0] = vec.view(torch.int32)
+        pairs[:, 1] = stamp
+        return pairs
+
+    # producer side: plain linear + two stamped copies
+    sig_seq = torch.tensor([6], dtype=torch.int32, device=DEV)
+    copies = [torch.zeros(m, 2, dtype=torch.int32, device=DEV) for _ in range(2)]
+    x = torch.from_numpy(lay["x"]).to(DEV)
+    prod = dict(y=torch.zeros(m, device=DEV), codes=codes, tlut=tl, workspace=ws(), x=x, signal_seq=sig_seq.data_ptr(),
+                signal_y=[c.data_ptr() for c in copies])
+    for it in (7, 8):
+        ops.linear_fused([prod], K, m, n, 1)
+        torch.cuda.synchronize()
+        assert int(sig_seq) == it
+        assert torch.equal(prod["y"].view(1, m), ops.decompress_matvec(codes, x, tl, K, m, n))
+        for c in copies:
+            assert torch.equal(c, stamped(prod["y"], it))
+
+    # consumer side
+    parts = [torch.randn(n, generator=g).to(DEV) for _ in range(2)]
+    sv_prev = (torch.randn(n, generator=g).sign() * 0.4).to(DEV)
+    res = torch.randn(n, generator=g).half().to(DEV)
+    w = (1 + 0.1 * torch.randn(n, generator=g)).half().to(DEV)
+    SU = torch.from_numpy(lay["SU"]).to(DEV)
+    common = dict(codes=codes, tlut=tl, residual=res, norm_weight=w, sign_in=SU, in_scale=1 / (math.sqrt(n) * 32), eps=1e-5,
+                  in_y_sign=sv_prev, in_y_scale=1 / math.sqrt(n))
+    want = dict(common, y=torch.zeros(m, device=DEV), workspace=ws(), in_y=parts[0] + parts[1])
+    ops.linear_fused([want], K, m, n, 1)
+    seq = torch.tensor([5], dtype=torch.int32, device=DEV)
+    vecs = [stamped(parts[0], 5), stamped(parts[1], 5)]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = dict(common, y=torch.zeros(m, device=DEV), workspace=ws(), peer_y=[v.data_ptr() for v in vecs],
+               peer_seq=seq.data_ptr(), peer_status=status.data_ptr())
+    ops.linear_fused([got], K, m, n, 1)
+    torch.cuda.synchronize()
+    assert int(status) == 0 and torch.equal(got["y"], want["y"])
+    # one value with an old stamp: the wait runs out after 2000 re-reads, the kernel still terminates
+    vecs[1][1234, 1] = 4
+    got["peer_max_polls"] = 2000
+    ops.linear_fused([got], K, m, n, 1)
+    torch.cuda.synchronize()
+    assert int(status) == 1
+
+
 def test_quip_lib_op_under_graph_capture():
     """The torch op boundary (lib/codebook/__init__.py:68-93 upstream): eager call and CUDA-graph replay."""
     from qtip_b200 import codebook_ops
