@@ -334,23 +334,19 @@ __device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, i
     return o;
 }
 
-// E consecutive stamped values of one GPU's partial vector: re-read until every stamp is `want` (bounded)
+// E consecutive stamped values of one GPU's partial vector, read once; false if a stamp is not `want`
 template <int E>
-__device__ __forceinline__ bool loadE_stamped(const uint2 *p, size_t i, unsigned want, unsigned max_polls, float (&o)[E]) {
-    for (unsigned polls = 0;; polls++) {
-        bool ok = true;
+__device__ __forceinline__ bool loadE_stamped(const uint2 *p, size_t i, unsigned want, float (&o)[E]) {
+    bool ok = true;
 #pragma unroll
-        for (int k = 0; k < E; k += 2) {
-            uint4 q;
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p + i + k) : "memory");
-            o[k] = __uint_as_float(q.x); o[k + 1] = __uint_as_float(q.z);
-            ok = ok && q.y == want && q.w == want;
-        }
-        if (ok) return true;
-        if (polls >= max_polls) return false;
-        __nanosleep(1000);
+    for (int k = 0; k < E; k += 2) {
+        uint4 q;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p + i + k) : "memory");
+        o[k] = __uint_as_float(q.x); o[k + 1] = __uint_as_float(q.z);
+        ok = ok && q.y == want && q.w == want;
     }
+    return ok;
 }
 
 // Before the whole CTA reads the vectors, one warp watches 32 sample elements of each until they are current:
@@ -373,26 +369,34 @@ __device__ __forceinline__ void await_samples(const PeerIn &peer, int n, unsigne
 
 // Fused input side for n = 1024*E (E = 4, 8, 16): a thread owns E consecutive values, everything up to the
 // Walsh-Hadamard transform stays in registers (see fwht_regs), the result goes to xs in fragment order.
-template <int E>
+template <int E, bool TP>
 __device__ __forceinline__ void fused_input_regs(const FusedIn &I, const PeerIn &peer, int n, uint4 *xs, float *buf, float *warp_sums) {
     // ownership of the E consecutive values a thread works on: tid*E ("A"), or, after one fwht_regs,
     // (lane*32 + warp)*E ("B").  The transform maps A to B and B to A, every other step is element-wise or
     // a sum over everything, so the deferred-producer path simply does its element-wise work in B.
-    const bool deferred = I.y_prev != nullptr || peer.n > 0;
+    const bool use_peers = TP && peer.n > 0;
+    const bool deferred = I.y_prev != nullptr || use_peers;
     const size_t jA = (size_t)threadIdx.x * E;
     const size_t jB = (size_t)((threadIdx.x & 31) * 32 + (threadIdx.x >> 5)) * E;
     const size_t j = deferred ? jB : jA;
     float v[E], rs[E], wn[E], gt[E], sg[E];
     // all operand vectors are requested before any is used
-    if (peer.n > 0) {
+    if (use_peers) {
         const unsigned want = *reinterpret_cast<const volatile unsigned *>(peer.seq);
         await_samples(peer, n, want);
-        bool ok = loadE_stamped<E>(peer.y[0], jA, want, peer.max_polls, v);
-        for (int p = 1; p < peer.n; p++) {      // same order on every GPU: the sums are bit-identical
-            float t[E];
-            ok = loadE_stamped<E>(peer.y[p], jA, want, peer.max_polls, t) && ok;
+        // A warp reads, checks and - for stragglers - retries as a unit: the loop is uniform over the warp (vote), so
+        // no lane ever spins on its own while its warp waits for it, and it ends after max_polls rounds at the latest.
+        bool ok;
+        for (unsigned round = 0;; round++) {
+            ok = loadE_stamped<E>(peer.y[0], jA, want, v);
+            for (int p = 1; p < peer.n; p++) {      // same order on every GPU: the sums are bit-identical
+                float t[E];
+                ok = loadE_stamped<E>(peer.y[p], jA, want, t) && ok;
 #pragma unroll
-            for (int k = 0; k < E; k++) v[k] += t[k];
+                for (int k = 0; k < E; k++) v[k] += t[k];
+            }
+            if (__all_sync(kFullMask, ok) || round >= peer.max_polls) break;
+            __nanosleep(200);
         }
         if (!ok) atomicOr(peer.status, 1u);
     } else if (deferred) loadE_f32<E>(I.y_prev, jA, v, true);
@@ -467,7 +471,8 @@ __device__ __forceinline__ void fused_output_regs(const FusedOut &O, const float
 // DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
 // D:  software-pipeline depth - each warp keeps D of its blocks' codes in flight in registers.
 // blockIdx.y selects the problem of the batch (all problems have the same m, n, K, bs).
-template <int K, bool XS, bool DB, int D>
+// TP: the tensor-parallel fields (PeerIn / Signal) are live; the single-GPU instantiation carries none of that code.
+template <int K, bool XS, bool DB, int D, bool TP>
 __global__ void __launch_bounds__(kThreads, 1)
     matvec_hyb_kernel(const __grid_constant__ MatvecBatch batch, int m, int n, int bs, int kmax, int mode) {
     constexpr int kBlockBytes = 128 * K;
@@ -526,16 +531,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
     // tensor parallelism: the stamp of this launch's result values (every CTA reads the counter before any CTA can
     // have taken its exit ticket, and only the last ticket holder advances it)
-    const unsigned stamp = P.sig.seq ? *reinterpret_cast<const volatile unsigned *>(P.sig.seq) + 1u : 0u;
+    unsigned stamp = 0u;
+    if constexpr (TP) stamp = P.sig.seq ? *reinterpret_cast<const volatile unsigned *>(P.sig.seq) + 1u : 0u;
     if constexpr (XS) {
         // xs[(b*nb + N)*4 + t] = { x[b][32N+2t..+1], x[..+8..], x[..+16..], x[..+24..] }
-        if (P.in.x_raw || P.in.y_prev || P.peer.n > 0) {
+        if (P.in.x_raw || P.in.y_prev || (TP && P.peer.n > 0)) {
             // fused input side (bs == 1, n a power of two): every CTA transforms the activation itself.
             // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
             // the whole prologue costs one L2 round trip, not one per array.
             const FusedIn &I = P.in;
-            if (n == 4096) fused_input_regs<4>(I, P.peer, n, xs, fscratch, sh->warp_sums);
-            else if (n == 8192) fused_input_regs<8>(I, P.peer, n, xs, fscratch, sh->warp_sums);
+            if (n == 4096) fused_input_regs<4, TP>(I, P.peer, n, xs, fscratch, sh->warp_sums);
+            else if (n == 8192) fused_input_regs<8, TP>(I, P.peer, n, xs, fscratch, sh->warp_sums);
             else {
             const int nvec = n >> 3;
             float ss = 0.f;
@@ -664,13 +670,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
         finish_segment<kConsumerWarps>(acc, DB ? red + (segno & 1) * red_floats : red, sh, out, partial, counters, M, nb,
-                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB, P.sig.copies, stamp);
+                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB, TP ? P.sig.copies : OutCopies{}, stamp);
         segno++;
         pos = npos;
         seg_end = nseg_end;
     }
 
-    if (P.sig.seq) {
+    if (TP && P.sig.seq) {
         // row-parallel partial result: the values are already on their way to every GPU (stamped); the CTA that
         // finishes last advances the sequence counter that the stamps of the next launch are derived from
         __syncthreads();
@@ -821,14 +827,14 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
     return QTIP_OK;
 }
 
-template <int K, bool XS, bool DB>
-int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
+template <int K, bool XS, bool DB, bool TP>
+int launch_hyb_variant_tp(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
     constexpr int D = K == 2 ? 4 : 2;  // blocks in flight per warp: 32 warps x D x 128K bytes = 32 KiB per SM
     static bool attr_set[64] = {};
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB, D, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kSmemLimit));
         attr_set[dev] = true;
     }
@@ -843,8 +849,16 @@ int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D>, batch, m, n, bs, p.kmax, p.mode));
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D, TP>, batch, m, n, bs, p.kmax, p.mode));
     return check_launch();
+}
+
+template <int K, bool XS, bool DB>
+int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
+    bool tp = false;
+    for (int i = 0; i < nprob; i++) tp = tp || batch.p[i].peer.n > 0 || batch.p[i].sig.seq != nullptr;
+    return tp ? launch_hyb_variant_tp<K, XS, DB, true>(batch, nprob, m, n, bs, smem_total, s)
+              : launch_hyb_variant_tp<K, XS, DB, false>(batch, nprob, m, n, bs, smem_total, s);
 }
 
 // fused_in: the batch uses the fused input transform (needs x staged in shared memory plus fp32 scratch)
