@@ -138,14 +138,33 @@ __global__ void __launch_bounds__(kSampleThreads)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // up to 32 logits per thread stay in registers for all rounds (vocabularies up to 32768); larger ones are re-read
+    constexpr int kHeld = 32;
+    const bool held = vocab <= kHeld * kSampleThreads;
+    float mine[kHeld];
+    if (held) {
+#pragma unroll
+        for (int j = 0; j < kHeld; j++) {
+            const int i = threadIdx.x + j * kSampleThreads;
+            mine[j] = i < vocab ? __ldcg(logits + i) : -INFINITY;
+        }
+    }
     for (int round = 0; round < top_k; round++) {
         float best = -INFINITY;
         int bi = 0x7FFFFFFF;
-        for (int i = threadIdx.x; i < vocab; i += kSampleThreads) {
-            const float v = __ldcg(logits + i);
-            bool taken = false;
-            for (int q = 0; q < round; q++) taken |= (top_idx[q] == i);
-            if (!taken && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+        if (held) {
+#pragma unroll
+            for (int j = 0; j < kHeld; j++) {
+                const float v = mine[j];
+                if (v > best) { best = v; bi = threadIdx.x + j * kSampleThreads; }    // ascending index: ties keep the lower
+            }
+        } else {
+            for (int i = threadIdx.x; i < vocab; i += kSampleThreads) {
+                const float v = __ldcg(logits + i);
+                bool taken = false;
+                for (int q = 0; q < round; q++) taken |= (top_idx[q] == i);
+                if (!taken && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -166,6 +185,12 @@ __global__ void __launch_bounds__(kSampleThreads)
             if (lane == 0) { top_val[round] = best; top_idx[round] = bi; }
         }
         __syncthreads();
+        if (held) {
+            const int win = top_idx[round];
+#pragma unroll
+            for (int j = 0; j < kHeld; j++)
+                if (win == threadIdx.x + j * kSampleThreads) mine[j] = -INFINITY;     // (a -inf logit can be drawn twice)
+        }
     }
     if (threadIdx.x == 0) {
         const int p = *pos;
