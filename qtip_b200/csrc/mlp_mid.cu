@@ -97,6 +97,7 @@ __host__ __device__ inline MidLayout mid_layout(int kfac, int len, int R) {
     return L;
 }
 
+// Built with -DQTIP_TRACE the kernel records globaltimer stamps at its phase boundaries (development aid).
 #ifdef QTIP_TRACE
 __device__ unsigned long long g_mid_trace[16];
 #define MID_STAMP(i) do { if (threadIdx.x == 0 && cluster_rank() == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_mid_trace[i] = t_; } } while (0)

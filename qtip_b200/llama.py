@@ -4,14 +4,17 @@ This is the measurement harness for end-to-end decode speed: a random-init model
 (`LlamaShape`), a static KV cache, and one CUDA graph per decode step, replayed once per token
 (upstream: eval/interactive_gen.py:42-85 with model/llama.py; the graph capture follows the pattern
 of lib/utils/graph_wrapper.py:16-47 instead of torch.compile).  Inside the graph a decoder layer of the
-Llama-2-7B shape is 8 launches of this library's kernels:
-    q,k,v in one launch (residual add, RMSNorm, input and output transforms fused)
-    RoPE + KV append     single-query attention
-    o_proj in one launch (both transforms fused)
-    gate,up in one launch (residual add, RMSNorm, input transform fused)   their output transform (11008 = 172*64)
-    input transform of down_proj with the SwiGLU product fused             down_proj (output transform fused)
-Widths that are not powers of two, and tensor-parallel row-parallel layers (all-reduce between matvec and
-output transform), fall back to separate transform launches.  The embedding lookup, the final norm + fp16 lm_head and the sampler are three small launches of the library as well.
+Llama-2-7B shape is 6 launches of this library's kernels:
+    q,k,v in one launch      (deferred output side of the previous down_proj, residual add, RMSNorm, input side)
+    attention                (output side of q/k/v, rotary embedding, KV append, single-query attention)
+    o_proj                   (input side fused; its output side is deferred into the next launch)
+    gate,up in one launch    (deferred output side of o_proj, residual add, RMSNorm, input side)
+    MLP middle               (output side of gate/up, SwiGLU product, input side of down_proj: 11008 = 172*64)
+    down_proj                (its output side is deferred into the next layer's q,k,v launch)
+plus three per token (embedding lookup, final norm + fp16 lm_head, sampler).  With tensor parallelism the partial
+results of o_proj / down_proj are summed inside the consuming launch through peer-mapped memory (qtip_b200/tp.py).
+Shapes the fused kernels do not cover (widths that are not 4096 / 8192, head counts that are not powers of two,
+factor widths with short rows) fall back to separate transform / rotary / attention launches.
 """
 import math
 from dataclasses import dataclass
