@@ -44,6 +44,17 @@ def shard_row_parallel(trellis, SU, SV, m, n, K, rank, tp):
     return t, SU[rank * n_r:(rank + 1) * n_r], SV, n_r
 
 
+def peer_addresses(base, width, rank):
+    """Device addresses of the stamped vectors, from the per-GPU base addresses of the symmetric allocation
+    (layout [slot 2][source GPU][width] x 8 bytes).  Returns (signal_y, peer_y), both indexed [slot][gpu]:
+    signal_y[slot][p] is where `rank` writes its vector on GPU p, peer_y[slot][p] is GPU p's vector in `rank`'s memory."""
+    world = len(base)
+    off = lambda slot, src: (slot * world + src) * width * 8   # noqa: E731
+    signal_y = [[base[p] + off(slot, rank) for p in range(world)] for slot in (0, 1)]
+    peer_y = [[base[rank] + off(slot, p) for p in range(world)] for slot in (0, 1)]
+    return signal_y, peer_y
+
+
 class PeerBuffers:
     """Peer-mapped vectors for the two row-parallel linears of a decoder layer.
 
@@ -67,9 +78,7 @@ class PeerBuffers:
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group.group_name if group is not None else dist.group.WORLD.group_name)
         base = [int(p) for p in self.handle.buffer_ptrs]
-        off = lambda slot, src: (slot * world + src) * width * 8          # byte offset of vector [slot][src]  # noqa: E731
-        self._signal_y = [[base[p] + off(slot, rank) for p in range(world)] for slot in (0, 1)]   # my vector, everywhere
-        self._peer_y = [[base[rank] + off(slot, p) for p in range(world)] for slot in (0, 1)]     # all local
+        self._signal_y, self._peer_y = peer_addresses(base, width, rank)
         self.max_polls = int(os.environ.get("QTIP_PEER_MAX_POLLS", 1 << 23))   # default ~10 s: ranks may start seconds apart
         self.seq = torch.zeros(2, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)

@@ -90,3 +90,20 @@ def test_shard_shapes():
         assert torch.equal(back, tr)
     with pytest.raises(AssertionError):
         tp.shard_column_parallel(tr, SU, SV, m, n, K, 0, 16)
+
+
+def test_peer_address_layout():
+    """Every (slot, source, destination) triple names one vector, producers and consumers agree on it, and the
+    vectors of one GPU tile its buffer without overlap."""
+    from qtip_b200 import tp
+    world, width = 4, 4096
+    base = [0x7000_0000_0000 + g * 0x1000_0000 for g in range(world)]
+    tables = [tp.peer_addresses(base, width, r) for r in range(world)]
+    for slot in (0, 1):
+        for src in range(world):
+            for dst in range(world):
+                # where src writes on dst == where dst reads src's vector
+                assert tables[src][0][slot][dst] == tables[dst][1][slot][src]
+    for g in range(world):
+        offs = sorted(a - base[g] for slot in (0, 1) for a in tables[g][1][slot])
+        assert offs == [i * width * 8 for i in range(2 * world)]
