@@ -17,6 +17,8 @@ Shapes the fused kernels do not cover (widths that are not 4096 / 8192, head cou
 factor widths with short rows) fall back to separate transform / rotary / attention launches.
 """
 import math
+import os
+import sys
 from dataclasses import dataclass
 
 import torch
@@ -148,8 +150,17 @@ class QtipLlama:
         # tp > 1: the partial results of o_proj / down_proj stay where they are; the next launch on every GPU waits
         # for all GPUs' flags and adds the partial vectors through peer-mapped memory (no all-reduce launch)
         self.peers = None
-        if tp > 1 and self.defer_h:
-            self.peers = tp_mod.PeerBuffers(s.hidden, tp_rank, tp_size, group, dev)
+        if tp > 1 and self.defer_h and os.environ.get("QTIP_TP_PEER", "1") != "0":
+            # every rank must take the same path: agree on whether the peer-mapped buffers could be set up
+            import torch.distributed as dist
+            try:
+                peers = tp_mod.PeerBuffers(s.hidden, tp_rank, tp_size, group, dev)
+            except Exception as e:   # no symmetric memory on this system: all-reduce launches instead
+                print(f"qtip_b200: peer-mapped buffers unavailable ({e!r}); using NCCL all-reduce", file=sys.stderr)
+                peers = None
+            ok = torch.tensor([1 if peers is not None else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            self.peers = peers if int(ok) == 1 else None
         self.defer_qkv = self.fuse_in_h and all(w in (1024, 2048, 4096, 8192, 16384) for w in (H, KV))
         # ... or, with power-of-two head counts, inside the attention kernel itself (no rotary launch at all)
         self.attn_fused = self.fuse_in_h and s.head_dim == 128 and pow2(self.n_heads) and pow2(self.n_kv_heads)
