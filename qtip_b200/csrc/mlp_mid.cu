@@ -57,15 +57,6 @@ __device__ __forceinline__ void sign_fragment(const uint32_t *rowbits, int mt, i
     a[0] = pm1_pair(w0 >> s); a[1] = pm1_pair(w1 >> s); a[2] = pm1_pair(w0 >> (s + 8)); a[3] = pm1_pair(w1 >> (s + 8));
 }
 
-// fp32 -> fp16 head and fp16 remainder
-__device__ __forceinline__ void split_f32(float x, __half &hi, __half &lo) {
-    hi = __float2half_rn(x);
-    lo = __float2half_rn(x - __half2float(hi));
-}
-__device__ __forceinline__ uint32_t pack_h2(__half a, __half b) {
-    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
-}
-
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -189,9 +180,12 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
                 uint32_t hi[4], lo[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    __half h0, l0, h1, l1;
-                    split_f32(e0[q], h0, l0); split_f32(e1[q], h1, l1);
-                    hi[q] = pack_h2(h0, h1); lo[q] = pack_h2(l0, l1);
+                    // rows k (low half) and k+1 (high half) of one column: one packed conversion each for head and remainder
+                    const __half2 h2 = __floats2half2_rn(e0[q], e1[q]);
+                    const float2 back = __half22float2(h2);
+                    const __half2 l2 = __floats2half2_rn(e0[q] - back.x, e1[q] - back.y);
+                    hi[q] = *reinterpret_cast<const uint32_t *>(&h2);
+                    lo[q] = *reinterpret_cast<const uint32_t *>(&l2);
                 }
                 uint32_t *dst = planes1 + (size_t)(which * 2) * L.kp * L.ld + kpi * L.ld + 4 * jg;
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
