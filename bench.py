@@ -198,7 +198,7 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device(dev))
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    torch.cuda.manual_seed(1234)  # same sampler draws on every rank
+    torch.cuda.manual_seed(1234)  # (the sampler itself is keyed by the model seed and the position: same draws on every rank)
     # N > 1: the one sequence is decoded tensor-parallel over the N GPUs (column/row-parallel shards, per-GPU
     # Hadamard transforms, one NCCL all-reduce after o_proj and after down_proj)
     model = QtipLlama(shape, max_positions=args.prompt + 2 * (warmup + steps) + 8, device=dev, seed=3000,

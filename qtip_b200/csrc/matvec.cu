@@ -32,7 +32,8 @@
 // Launch overlap.  The kernel is launched with programmatic stream serialization: everything that
 // touches only weights (the first code loads, the table build) runs before griddepcontrol.wait,
 // i.e. while the previous kernel of the stream drains; x, out and the workspace are touched only
-// after it.  The kernel contains no spin-waits.
+// after it.  The single-GPU kernel contains no spin-waits; the tensor-parallel instantiation (TP) has one bounded
+// wait, for the other GPUs' result values (see PeerIn below).
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
 #include <cstdlib>
