@@ -391,7 +391,9 @@ def test_linear_fused_peer_sum_and_signal():
         ops.linear_fused([prod], K, m, n, 1)
         torch.cuda.synchronize()
         assert int(sig_seq) == it
-        assert torch.equal(prod["y"].view(1, m), ops.decompress_matvec(codes, x, tl, K, m, n))
+        # the plain launch runs 16 decoding warps, this one 32: same products, another summation order
+        plain = ops.decompress_matvec(codes, x, tl, K, m, n)
+        assert rel_l2(prod["y"].view(1, m).cpu().numpy(), plain.cpu().numpy()) < 2e-6
         for c in copies:
             assert torch.equal(c, stamped(prod["y"], it))
 
