@@ -45,8 +45,9 @@ def main():
     model.peers = peers
     assert torch.equal(fused_eager, fused_graph), "graph replay differs from eager"
     err = (fused_eager - nccl).abs().max().item() / nccl.abs().max().item()
-    # rank-ordered sum vs NCCL's order: identical for two ranks, last-bit differences of the fp32 partials beyond
-    assert err < (1e-6 if world == 2 else 2e-3), err
+    # the two runs add the same fp32 partial results in different orders (rank order vs NCCL's; 32 vs 16 decoding
+    # warps in down_proj): last-bit differences that fp16 roundings further down may turn into a flipped bit
+    assert err < 2e-3, err
     # every rank computed the same logits
     ref = fused_eager.clone()
     dist.broadcast(ref, 0)
