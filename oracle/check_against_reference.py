@@ -1,6 +1,6 @@
 """Pin the numpy oracle against the upstream torch implementation (CPU).
 
-Needs the upstream QTIP tree (QTIP_REFERENCE_ROOT, default /root/reference); run by hand:
+Needs a checkout of the upstream QTIP tree (environment variable QTIP_REFERENCE_ROOT); run by hand:
     python oracle/check_against_reference.py
 It is not collected by pytest and nothing at run time depends on it; the fixtures under
 tests/golden/ carry the same comparisons to machines without the upstream tree.
