@@ -107,3 +107,62 @@ def test_peer_address_layout():
     for g in range(world):
         offs = sorted(a - base[g] for slot in (0, 1) for a in tables[g][1][slot])
         assert offs == [i * width * 8 for i in range(2 * world)]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_stamped_vector_protocol_never_loses_a_round(world):
+    """Model of the tensor-parallel protocol of qtip_linear_fused (signal_* / peer_* fields) with ranks that advance
+    in arbitrary interleavings: per layer a rank runs producer(slot 0), consumer(slot 0), producer(slot 1) and, in
+    the next layer, consumer(slot 1); the last layer's slot-1 result goes through an ordinary all-reduce (a point
+    where all ranks meet).  A producer stamps its vector on every rank with its sequence counter + 1 and then
+    advances the counter; a consumer needs every rank's vector to carry exactly its own counter value.  The check:
+    whenever a consumer can run, no vector it needs has already been overwritten by a later round (the stamps are
+    equal, never ahead), for every schedule tried."""
+    import random
+    layers, tokens = 3, 3
+    program = []                                   # one rank's launches of one token
+    for li in range(layers):
+        if li > 0:
+            program.append(("consume", 1))
+        program.append(("produce", 0))
+        program.append(("consume", 0))
+        program.append(("produce", 1) if li != layers - 1 else ("allreduce", None))
+    rng = random.Random(world)
+    for trial in range(200):
+        seq = [[0, 0] for _ in range(world)]                                   # per rank, per slot
+        stamp = [[[0] * world for _ in range(2)] for _ in range(world)]        # stamp[holder][slot][source]
+        pc = [0] * world
+        total = len(program) * tokens
+        at_allreduce = set()
+        while any(p < total for p in pc):
+            runnable = []
+            for r in range(world):
+                if pc[r] >= total:
+                    continue
+                op, slot = program[pc[r] % len(program)]
+                if op == "consume":
+                    have = stamp[r][slot]
+                    assert all(s <= seq[r][slot] for s in have), "a vector was overwritten before it was read"
+                    if all(s == seq[r][slot] for s in have):
+                        runnable.append(r)
+                elif op == "allreduce":
+                    at_allreduce.add(r)
+                    if len(at_allreduce) == world:
+                        runnable.append(r)
+                else:
+                    runnable.append(r)
+            assert runnable, "deadlock"
+            r = rng.choice(runnable)
+            op, slot = program[pc[r] % len(program)]
+            if op == "produce":
+                s = seq[r][slot] + 1
+                for holder in range(world):
+                    stamp[holder][slot][r] = s
+                seq[r][slot] = s
+            elif op == "allreduce":
+                for q in range(world):                # every rank leaves the collective together
+                    assert program[pc[q] % len(program)][0] == "allreduce"
+                    pc[q] += 1
+                at_allreduce.clear()
+                continue
+            pc[r] += 1
