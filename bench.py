@@ -23,7 +23,7 @@ sys.path.insert(0, ROOT)
 METRIC = "bs=1 decode tok/s (Llama-2-7B-shape, 2-bit HYB)"
 PROMPT_TOKENS = 128
 PUBLISHED_TOK_S = 188.0  # upstream README.md:31-38, Llama-2-7B 2-bit on an RTX 6000 Ada (fused q/k/v and up/gate)
-# DRAM bytes (read + write) of one decode-matvec launch from an ncu capture (profiles/matvec_hyb_llama7b_k2.md)
+# DRAM bytes (read + write) of one decode-matvec launch, from an ncu capture of the same kernel
 NCU_TRAFFIC_BYTES = {(4096, 4096): 4283136, (11008, 4096): 11361280, (4096, 11008): 11375872}
 
 

@@ -229,10 +229,18 @@ int qtip_mlp_mid(void *out, const float *y_gate, const float *y_up, const float 
  * token position in device memory (read at run time, so a captured graph can be replayed).
  * ------------------------------------------------------------------------------------------ */
 
+/* Capacity guards of the decode-loop entry points below.  The token index and the position live in device memory
+ * (so that one captured graph serves every step) and the host cannot check them per launch; every entry point
+ * that uses one as an address therefore takes the capacity of the buffer it indexes (vocab, max_positions,
+ * max_tokens) and an optional `status` word (one zero-initialised uint32 in device memory, may be NULL).  A kernel
+ * that finds the index outside its buffer touches nothing, ORs a bit into *status (1: position outside the KV
+ * cache, 2: token outside the embedding table, 4: token log full) and returns; the context stays usable. */
+
 /* Embedding lookup for one token: res (hidden) fp16 = embed[*token] (embed is (vocab, hidden) fp16, token a
  * 64-bit index in device memory); delta (hidden) fp16 = 0.  Replaces embed_tokens of LlamaModel.forward
  * (model/llama.py) for the decode loop.  hidden a multiple of 8, pointers 16-byte aligned. */
-int qtip_embed_token(void *res, void *delta, const void *embed, const long long *token, int hidden, void *stream);
+int qtip_embed_token(void *res, void *delta, const void *embed, const long long *token, int hidden, int vocab,
+                     unsigned *status, void *stream);
 
 /* Final RMSNorm and the (unquantized, fp16) lm_head for one token:
  * logits (vocab) fp32 = weight (vocab, hidden) @ fp16( norm_weight * fp16( RMSNorm(res + delta) ) ), the tail of
@@ -242,17 +250,20 @@ int qtip_lm_head(float *logits, const void *res, const void *delta, const void *
 
 /* Temperature / top-k sampling without a host synchronisation (eval/interactive_gen.py:15-40: logits_to_probs +
  * multinomial_sample_one_no_sync): the top_k (<= 16) largest logits, softmax(top / temperature), one draw from a
- * counter-based generator keyed by (seed, *pos).  Writes the token to *token and out_tokens[*pos + 1] and
- * advances *pos (32-bit, device memory).  The draw is reproducible for a given seed but is not torch's stream. */
+ * counter-based generator keyed by (seed, *pos).  Writes the token to *token and out_tokens[*pos + 1] (out_tokens
+ * holds max_tokens entries) and advances *pos (32-bit, device memory).  The draw is reproducible for a given seed
+ * but is not torch's stream. */
 int qtip_sample_top_k(long long *token, long long *out_tokens, int *pos, const float *logits, int vocab,
-                      float temperature, int top_k, unsigned long long seed, void *stream);
+                      float temperature, int top_k, unsigned long long seed, int max_tokens, unsigned *status,
+                      void *stream);
 
 /* Rotary embedding of q (n_heads, head_dim; in place) and k (n_kv_heads, head_dim), and append of the
  * rotated k and of v to the caches at row *pos (caches are (max_positions, n_kv_heads*head_dim)).
  * Replaces apply_rotary_pos_emb + StaticCache.update (model/llama.py:797-898,
  * model/cache_utils.py:1147-1193) for a single new token. */
 int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, void *cache_v, const int *pos,
-                        int n_heads, int n_kv_heads, int head_dim, float theta, void *stream);
+                        int n_heads, int n_kv_heads, int head_dim, float theta, int max_positions, unsigned *status,
+                        void *stream);
 
 /* qtip_rope_kv_append with the output side of the q / k / v linears in front of it: y_q / y_k / y_v are the raw
  * fp32 results of the three matvecs (e.g. the y of a qtip_linear_fused launch without fused output side); the
@@ -263,7 +274,7 @@ int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, vo
 int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
                               const float *sign_k, const float *sign_v, float scale_q, float scale_kv, void *cache_k,
                               void *cache_v, const int *pos, int n_heads, int n_kv_heads, int head_dim, float theta,
-                              void *stream);
+                              int max_positions, unsigned *status, void *stream);
 
 /* qtip_rope_kv_append_fused and qtip_attn_decode in one launch: from the raw fp32 results of the q / k / v matvecs
  * to the attention output (n_heads, head_dim) fp16 for one new token at row *pos, appending the rotated k and v
@@ -272,14 +283,14 @@ int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, c
 int qtip_attn_decode_fused(void *out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
                            const float *sign_k, const float *sign_v, float scale_q, float scale_kv, void *cache_k,
                            void *cache_v, const int *pos, int n_heads, int n_kv_heads, int head_dim, float theta,
-                           void *stream);
+                           int max_positions, unsigned *status, void *stream);
 
 /* Single-query attention over cache rows 0..*pos: out (n_heads, head_dim).  head_dim must be 128;
  * q and the caches 16-byte aligned.
  * Replaces the scaled_dot_product_attention call of LlamaSdpaAttention.forward (model/llama.py:884-891)
  * for a single new token. */
 int qtip_attn_decode(void *out, const void *q, const void *cache_k, const void *cache_v, const int *pos, int n_heads,
-                     int n_kv_heads, int head_dim, void *stream);
+                     int n_kv_heads, int head_dim, int max_positions, unsigned *status, void *stream);
 
 #ifdef __cplusplus
 }

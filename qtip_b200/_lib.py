@@ -45,13 +45,14 @@ SIGNATURES = {
     "qtip_mlp_mid_table_bytes": (_sz, []),
     "qtip_mlp_mid_prepare": (_i, [_vp, _vp, _i, _i, _vp]),
     "qtip_mlp_mid": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp]),
-    "qtip_embed_token": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "qtip_embed_token": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "qtip_lm_head": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
-    "qtip_sample_top_k": (_i, [_vp, _vp, _vp, _vp, _i, _f, _i, ctypes.c_ulonglong, _vp]),
-    "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
-    "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
-    "qtip_attn_decode_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
-    "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "qtip_sample_top_k": (_i, [_vp, _vp, _vp, _vp, _i, _f, _i, ctypes.c_ulonglong, _i, _vp, _vp]),
+    "qtip_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _vp]),
+    "qtip_rope_kv_append_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp,
+                                       _vp]),
+    "qtip_attn_decode_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _vp]),
+    "qtip_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
 
 _lib = None

@@ -10,16 +10,27 @@
 namespace qtip {
 namespace {
 
+// Cache capacity guard: a position outside [0, max_pos) must not be used as a cache row.  The whole grid sees the
+// same position, so every CTA leaves together (before any barrier that later code relies on); the caller learns
+// of it through the status word.
+__device__ __forceinline__ bool position_ok(int pos, int max_pos, unsigned *status) {
+    if ((unsigned)pos < (unsigned)max_pos) return true;
+    if (status && threadIdx.x == 0) atomicOr(status, 1u);
+    return false;
+}
+
 // q: (n_heads, hd) fp16 rotated in place.  k: (n_kv, hd) rotated and appended to cache_k[pos];
 // v: (n_kv, hd) appended to cache_v[pos].  Caches are (max_pos, n_kv*hd) fp16.
 // HF convention: out[i] = x[i]*cos - x[i+hd/2]*sin ; out[i+hd/2] = x[i+hd/2]*cos + x[i]*sin,
 // angle = pos * theta^(-2i/hd).
 __global__ void rope_kv_kernel(__half *__restrict__ q, const __half *__restrict__ k, const __half *__restrict__ v,
                                __half *__restrict__ cache_k, __half *__restrict__ cache_v,
-                               const int *__restrict__ pos_ptr, int n_heads, int n_kv, int hd, float log2_theta) {
+                               const int *__restrict__ pos_ptr, int n_heads, int n_kv, int hd, float log2_theta,
+                               int max_pos, unsigned *status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int pos = *pos_ptr;
+    if (!position_ok(pos, max_pos, status)) return;
     const int half = hd >> 1;
     const int total = (n_heads + n_kv) * half;
     const size_t crow = (size_t)pos * n_kv * hd;
@@ -58,6 +69,8 @@ struct QkvPostArgs {
     const int *pos;
     int n_heads, n_kv, hd;
     float log2_theta;
+    int max_pos;
+    unsigned *status;
 };
 
 template <int E>
@@ -91,6 +104,7 @@ __global__ void __launch_bounds__(1024) qkv_post_kernel(const QkvPostArgs a) {
         default: qkv_transform<16>(a, which, buf, vals); break;
     }
     const int pos = *a.pos, hd = a.hd, half = hd >> 1;
+    if (!position_ok(pos, a.max_pos, a.status)) return;
     const size_t crow = (size_t)pos * a.n_kv * hd;
     if (which == 2) {
         for (int e = threadIdx.x * 2; e < width; e += blockDim.x * 2)
@@ -127,7 +141,7 @@ __device__ __forceinline__ void unpack8(const uint4 &r, float (&f)[8]) {
 __global__ void __launch_bounds__(kAttnThreads)
     attn_decode_kernel(__half *__restrict__ out, const __half *__restrict__ q, const __half *__restrict__ cache_k,
                        const __half *__restrict__ cache_v, const int *__restrict__ pos_ptr, int n_heads, int n_kv,
-                       float scale) {
+                       float scale, int max_pos, unsigned *status) {
     constexpr int hd = 128, G = kAttnGroups, U = kAttnBatch;
     __shared__ float sc[kAttnChunk];
     __shared__ float red_max[kAttnThreads / 32], red_sum[kAttnThreads / 32];
@@ -136,6 +150,7 @@ __global__ void __launch_bounds__(kAttnThreads)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, kvh = head / (n_heads / n_kv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, grp = tid >> 4, sub = tid & 15;
+    if (!position_ok(*pos_ptr, max_pos, status)) return;
     const int ctx = *pos_ptr + 1;
     const size_t row = (size_t)n_kv * hd;
     float qv[8];
@@ -258,6 +273,8 @@ struct AttnFusedArgs {
     const int *pos;
     int n_heads, n_kv;
     float log2_theta, softmax_scale;
+    int max_pos;
+    unsigned *status;
 };
 
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_fused_kernel(const AttnFusedArgs a) {
@@ -272,6 +289,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_fused_kernel(const A
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int pos = *a.pos;
+    if (!position_ok(pos, a.max_pos, a.status)) return;
 
     // ---- signed sums over heads: thread (quarter, d) adds a quarter of the heads (all three loads batches in flight)
     {
@@ -467,21 +485,23 @@ int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t s, A
 using namespace qtip;
 
 extern "C" int qtip_rope_kv_append(void *q, const void *k, const void *v, void *cache_k, void *cache_v, const int *pos,
-                                   int n_heads, int n_kv_heads, int head_dim, float theta, void *stream) {
-    if (!q || !k || !v || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+                                   int n_heads, int n_kv_heads, int head_dim, float theta, int max_positions,
+                                   unsigned *status, void *stream) {
+    if (!q || !k || !v || !cache_k || !cache_v || !pos || max_positions <= 0) return QTIP_ERR_BAD_ARG;
     if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
     const int total = (n_heads + n_kv_heads) * (head_dim / 2);
     return launch_pdl(rope_kv_kernel, dim3((total + 255) / 256), dim3(256), static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
                       static_cast<__half *>(cache_k), static_cast<__half *>(cache_v), pos, n_heads, n_kv_heads, head_dim,
-                      log2f(theta));
+                      log2f(theta), max_positions, status);
 }
 
 extern "C" int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const float *y_k, const float *y_v,
                                          const float *sign_q, const float *sign_k, const float *sign_v, float scale_q,
                                          float scale_kv, void *cache_k, void *cache_v, const int *pos, int n_heads,
-                                         int n_kv_heads, int head_dim, float theta, void *stream) {
-    if (!q_out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+                                         int n_kv_heads, int head_dim, float theta, int max_positions,
+                                         unsigned *status, void *stream) {
+    if (!q_out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos || max_positions <= 0) return QTIP_ERR_BAD_ARG;
     if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
     const int wq = n_heads * head_dim, wkv = n_kv_heads * head_dim;
     auto ok_width = [](int w) { return w == 1024 || w == 2048 || w == 4096 || w == 8192 || w == 16384; };
@@ -496,6 +516,7 @@ extern "C" int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const fl
     a.width[0] = wq; a.width[1] = wkv; a.width[2] = wkv;
     a.q_out = static_cast<__half *>(q_out); a.cache_k = static_cast<__half *>(cache_k); a.cache_v = static_cast<__half *>(cache_v);
     a.pos = pos; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.hd = head_dim; a.log2_theta = log2f(theta);
+    a.max_pos = max_positions; a.status = status;
     const size_t smem = (size_t)(2 * wq + 128) * sizeof(float);
     static bool attr_set[64] = {};
     int dev = 0;
@@ -519,20 +540,22 @@ extern "C" int qtip_rope_kv_append_fused(void *q_out, const float *y_q, const fl
 }
 
 extern "C" int qtip_attn_decode(void *out, const void *q, const void *cache_k, const void *cache_v, const int *pos,
-                                int n_heads, int n_kv_heads, int head_dim, void *stream) {
-    if (!out || !q || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+                                int n_heads, int n_kv_heads, int head_dim, int max_positions, unsigned *status,
+                                void *stream) {
+    if (!out || !q || !cache_k || !cache_v || !pos || max_positions <= 0) return QTIP_ERR_BAD_ARG;
     if (head_dim != 128 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
     if (!aligned(q, 16) || !aligned(cache_k, 16) || !aligned(cache_v, 16)) return QTIP_ERR_ALIGNMENT;
     return launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(kAttnThreads), static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(out), static_cast<const __half *>(q), static_cast<const __half *>(cache_k),
-                      static_cast<const __half *>(cache_v), pos, n_heads, n_kv_heads, 1.0f / sqrtf((float)head_dim));
+                      static_cast<const __half *>(cache_v), pos, n_heads, n_kv_heads, 1.0f / sqrtf((float)head_dim),
+                      max_positions, status);
 }
 
 extern "C" int qtip_attn_decode_fused(void *out, const float *y_q, const float *y_k, const float *y_v, const float *sign_q,
                                       const float *sign_k, const float *sign_v, float scale_q, float scale_kv,
                                       void *cache_k, void *cache_v, const int *pos, int n_heads, int n_kv_heads,
-                                      int head_dim, float theta, void *stream) {
-    if (!out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos) return QTIP_ERR_BAD_ARG;
+                                      int head_dim, float theta, int max_positions, unsigned *status, void *stream) {
+    if (!out || !y_q || !y_k || !y_v || !cache_k || !cache_v || !pos || max_positions <= 0) return QTIP_ERR_BAD_ARG;
     if (head_dim != 128 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return QTIP_ERR_BAD_SHAPE;
     if ((n_heads & (n_heads - 1)) || (n_kv_heads & (n_kv_heads - 1))) return QTIP_ERR_BAD_SHAPE;   // Hadamard over heads
     if (!aligned(cache_k, 16) || !aligned(cache_v, 16) || !aligned(y_q, 4)) return QTIP_ERR_ALIGNMENT;
@@ -542,5 +565,6 @@ extern "C" int qtip_attn_decode_fused(void *out, const float *y_q, const float *
     a.out = static_cast<__half *>(out); a.cache_k = static_cast<__half *>(cache_k); a.cache_v = static_cast<__half *>(cache_v);
     a.pos = pos; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.log2_theta = log2f(theta);
     a.softmax_scale = 1.0f / sqrtf((float)head_dim);
+    a.max_pos = max_positions; a.status = status;
     return launch_pdl(attn_decode_fused_kernel, dim3(n_heads), dim3(kAttnThreads), static_cast<cudaStream_t>(stream), a);
 }

@@ -11,10 +11,15 @@ namespace {
 
 // res = embed[token]; delta = 0 (the residual update pending for the first layer)
 __global__ void embed_kernel(__half *__restrict__ res, __half *__restrict__ delta, const __half *__restrict__ embed,
-                             const long long *__restrict__ token, int hidden) {
+                             const long long *__restrict__ token, int hidden, int vocab, unsigned *status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)(*token) * hidden);
+    const long long tok = *token;
+    if (tok < 0 || tok >= vocab) {            // not a row of the table: leave res / delta alone and report
+        if (status && threadIdx.x == 0) atomicOr(status, 2u);
+        return;
+    }
+    const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)tok * hidden);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden / 8; i += gridDim.x * blockDim.x) {
         reinterpret_cast<uint4 *>(res)[i] = __ldg(src + i);
         reinterpret_cast<uint4 *>(delta)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -130,7 +135,8 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
 // Writes the token to `token` and to out_tokens[*pos + 1], then advances *pos.
 __global__ void __launch_bounds__(kSampleThreads)
     sample_kernel(long long *__restrict__ token, long long *__restrict__ out_tokens, int *__restrict__ pos,
-                  const float *__restrict__ logits, int vocab, float inv_temperature, int top_k, unsigned long long seed) {
+                  const float *__restrict__ logits, int vocab, float inv_temperature, int top_k, unsigned long long seed,
+                  int max_tokens, unsigned *status) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ float top_val[kMaxTopK];
@@ -206,7 +212,8 @@ __global__ void __launch_bounds__(kSampleThreads)
         }
         const long long t = top_idx[pick];
         *token = t;
-        out_tokens[p + 1] = t;
+        if (p >= 0 && p + 1 < max_tokens) out_tokens[p + 1] = t;      // the token log is full: keep sampling, report
+        else if (status) atomicOr(status, 4u);
         *pos = p + 1;
     }
 }
@@ -232,12 +239,13 @@ int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cuda
 
 using namespace qtip;
 
-extern "C" int qtip_embed_token(void *res, void *delta, const void *embed, const long long *token, int hidden, void *stream) {
-    if (!res || !delta || !embed || !token) return QTIP_ERR_BAD_ARG;
+extern "C" int qtip_embed_token(void *res, void *delta, const void *embed, const long long *token, int hidden, int vocab,
+                                unsigned *status, void *stream) {
+    if (!res || !delta || !embed || !token || vocab <= 0) return QTIP_ERR_BAD_ARG;
     if (hidden <= 0 || (hidden & 7)) return QTIP_ERR_BAD_SHAPE;
     if (!aligned(res, 16) || !aligned(delta, 16) || !aligned(embed, 16) || !aligned(token, 8)) return QTIP_ERR_ALIGNMENT;
     return launch_pdl(embed_kernel, dim3(2), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<__half *>(res),
-                      static_cast<__half *>(delta), static_cast<const __half *>(embed), token, hidden);
+                      static_cast<__half *>(delta), static_cast<const __half *>(embed), token, hidden, vocab, status);
 }
 
 extern "C" int qtip_lm_head(float *logits, const void *res, const void *delta, const void *norm_weight, const void *weight,
@@ -265,10 +273,11 @@ extern "C" int qtip_lm_head(float *logits, const void *res, const void *delta, c
 }
 
 extern "C" int qtip_sample_top_k(long long *token, long long *out_tokens, int *pos, const float *logits, int vocab,
-                                 float temperature, int top_k, unsigned long long seed, void *stream) {
-    if (!token || !out_tokens || !pos || !logits) return QTIP_ERR_BAD_ARG;
+                                 float temperature, int top_k, unsigned long long seed, int max_tokens, unsigned *status,
+                                 void *stream) {
+    if (!token || !out_tokens || !pos || !logits || max_tokens <= 0) return QTIP_ERR_BAD_ARG;
     if (vocab <= 0 || top_k < 1 || top_k > kMaxTopK || top_k > vocab) return QTIP_ERR_BAD_SHAPE;
     const float inv_t = 1.0f / fmaxf(temperature, 1e-5f);
     return launch_pdl(sample_kernel, dim3(1), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), token, out_tokens, pos,
-                      logits, vocab, inv_t, top_k, seed);
+                      logits, vocab, inv_t, top_k, seed, max_tokens, status);
 }

@@ -36,7 +36,6 @@
 // wait, for the other GPUs' result values (see PeerIn below).
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
-#include <cstdlib>
 #include <mutex>
 
 #include "fwht.cuh"
@@ -82,7 +81,6 @@ constexpr long kTailBytes = 40 * 1024;
 
 // nprob problems of the same shape share one launch: each gets sm_count / nprob CTAs.
 Partition make_partition(int m, int n, int K, int nprob = 1) {
-    static const int forced = [] { const char *e = getenv("QTIP_MATVEC_MODE"); return e ? atoi(e) : 0; }();
     Partition p;
     const long mb = m >> 5, nb = n >> 5, B = mb * nb, bb = 128 * K;
     const long sms = sm_count() / nprob > 0 ? sm_count() / nprob : 1;
@@ -90,7 +88,7 @@ Partition make_partition(int m, int n, int K, int nprob = 1) {
     const long cost_rows = ((mb + g_rows - 1) / g_rows) * nb * bb;
     const bool shared_rows = (B % g_stream) != 0 || ((B / g_stream) % nb) != 0;
     const long cost_stream = ((B + g_stream - 1) / g_stream) * bb + (shared_rows ? kTailBytes : 0);
-    p.mode = forced ? forced : (cost_rows <= cost_stream ? kModeRows : kModeStreamK);
+    p.mode = cost_rows <= cost_stream ? kModeRows : kModeStreamK;
     p.grid = (int)(p.mode == kModeRows ? g_rows : g_stream);
     p.kmax = max_contributors(nb, B, g_stream);
     return p;

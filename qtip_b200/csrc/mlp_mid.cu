@@ -88,13 +88,6 @@ __host__ __device__ inline MidLayout mid_layout(int kfac, int len, int R) {
     return L;
 }
 
-// Built with -DQTIP_TRACE the kernel records globaltimer stamps at its phase boundaries (development aid).
-#ifdef QTIP_TRACE
-__device__ unsigned long long g_mid_trace[16];
-#define MID_STAMP(i) do { if (threadIdx.x == 0 && cluster_rank() == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_mid_trace[i] = t_; } } while (0)
-#else
-#define MID_STAMP(i)
-#endif
 
 // The bit rows every CTA of the cluster needs, derived once per factor matrix:
 // table[rank][0][il] = row (rank*R + il) of S, table[rank][1][il] = column (rank*R + il) of S, zero beyond kfac.
@@ -133,8 +126,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
     uint32_t *planes1 = smw + L.planes1, *planes2 = smw + L.planes2;
     float *tbuf = reinterpret_cast<float *>(smw + L.tbuf);
     constexpr int ldt = len + 4;
-
-    MID_STAMP(0);
     // ---- phase 0: weights only, all asynchronous (waited for before phase 2)
     for (int c = tid; c < 2 * 32 * kRowWords / 4; c += kMidThreads) cp_async16(rb_out + c * 4, a.table + rank * 2 * 32 * kRowWords + c * 4);
     if (rows_here > 0) {
@@ -151,7 +142,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
     cluster_arrive();     // every CTA of the cluster is running; matched by the wait before the remote stores
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    MID_STAMP(1);
 
     // ---- phase 1: y_gate, y_up -> head / remainder planes, [k/2][j] words.  One item = (which, k pair, 4 columns);
     // a thread's items are all requested before the first is converted.
@@ -195,7 +185,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
-    MID_STAMP(2);
 
     // ---- phase 2: T[which][il][j] = sum_k S[i0+il][k] * y_which[k][j]
     {
@@ -218,7 +207,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
         }
     }
     __syncthreads();
-    MID_STAMP(3);
     cluster_wait();       // (arrive above) every CTA runs, so its shared memory may be written
 
     // ---- phase 3: one warp per own row: transform over j, signs, SwiGLU, sign; the fp16 result goes to the planes
@@ -241,7 +229,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
             reinterpret_cast<__half *>(planes2 + (row >> 1) * L.ld + lane + 32 * e)[row & 1] = av;
         }
     }
-    MID_STAMP(4);
     cluster_arrive();
     cluster_wait();       // every CTA has written its own rows into its own planes
     // pull the other CTAs' rows (16-byte distributed-shared-memory loads; same offsets in every CTA)
@@ -270,7 +257,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
     }
     cluster_arrive();     // this CTA no longer reads remote memory; matched by the wait at the end of the kernel
     __syncthreads();
-    MID_STAMP(5);
 
     // ---- phase 4: X'[il][j] = sum_i S[i][i0+il] * a[i][j]  (exact: +-1 times fp16, fp32 accumulation)
     {
@@ -301,7 +287,6 @@ __global__ void __launch_bounds__(kMidThreads, 1) mlp_mid_kernel(const MlpMidArg
         for (int e = 0; e < E; e++) a.out[(size_t)(i0 + warp) * len + lane + 32 * e] = __float2half_rn(v[e] * a.scale_in);
     }
     cluster_wait();       // nobody is still reading this CTA's shared memory
-    MID_STAMP(6);
 }
 
 int mid_rows_per_cta(int kfac, int cluster) {
@@ -352,11 +337,6 @@ int mid_cluster_size(int len) {
 
 using namespace qtip;
 
-#ifdef QTIP_TRACE
-extern "C" int qtip_mid_trace(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_mid_trace, sizeof(unsigned long long) * 16);
-}
-#endif
 
 extern "C" int qtip_mlp_mid_supported(int n, int kfac) {
     if (kfac <= 1 || kfac > kMaxFactor || (kfac & 3) || n <= 0 || n % kfac) return 0;

@@ -134,6 +134,9 @@ class QtipLlama:
         self.logits = torch.zeros(1, s.vocab, **f32)
         self.sample_seed = seed
         self.out_tokens = torch.zeros(max_positions + 1, dtype=torch.int64, device=dev)
+        # set by a kernel that found the position / token outside its buffer (the kernel then skipped its work)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.steps_done = 0   # host-side count of positions consumed since reset()
         need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
                    for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
@@ -213,7 +216,7 @@ class QtipLlama:
         s = self.shape
         H, KV, MLP = self.H, self.KV, self.MLP
         res_a, res_b = self.res
-        ops.embed_token(res_a, self.delta, self.embed, self.token)
+        ops.embed_token(res_a, self.delta, self.embed, self.token, status=self.status)
         inv_h, inv_hl, inv_m, inv_kv = (1 / math.sqrt(d) for d in (s.hidden, H, MLP, KV))
         bits = self.bits
         tp1 = self.tp == 1
@@ -255,17 +258,17 @@ class QtipLlama:
             if dq and self.attn_fused:
                 ops.attn_decode_fused(self.attn, y_q, y_k, y_v, L["q"].SV32, L["k"].SV32, L["v"].SV32, inv_hl, inv_kv,
                                       self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                                      s.head_dim, s.rope_theta)
+                                      s.head_dim, s.rope_theta, status=self.status)
             elif dq:
                 ops.rope_kv_append_fused(q, y_q, y_k, y_v, L["q"].SV32, L["k"].SV32, L["v"].SV32, inv_hl, inv_kv,
                                          self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                                         s.head_dim, s.rope_theta)
+                                         s.head_dim, s.rope_theta, status=self.status)
             else:
                 ops.rope_kv_append(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                                   s.head_dim, s.rope_theta)
+                                   s.head_dim, s.rope_theta, status=self.status)
             if not (dq and self.attn_fused):
                 ops.attn_decode(self.attn, q, self.cache_k[li], self.cache_v[li], self.pos, self.n_heads, self.n_kv_heads,
-                                s.head_dim)
+                                s.head_dim, status=self.status)
             # ---- o_proj (row-parallel: local chunk in, full-length partial out, all-reduce, transform)
             defer = self.defer_h
             use_peers = defer and self.peers is not None
@@ -346,7 +349,8 @@ class QtipLlama:
                                   kfac=self.kf_h, scale=inv_h)
         # ---- final norm + lm_head (fp16 weights, HBM-bound GEMV), sampler: token, out_tokens[pos + 1], pos += 1
         ops.lm_head(self.logits, res_a, self.delta, self.ln_f, self.lm_head, s.rms_eps)
-        ops.sample_top_k(self.token, self.out_tokens, self.pos, self.logits, temperature=0.6, top_k=5, seed=self.sample_seed)
+        ops.sample_top_k(self.token, self.out_tokens, self.pos, self.logits, temperature=0.6, top_k=5, seed=self.sample_seed,
+                         status=self.status)
 
     # -- driving ----------------------------------------------------------------------------------
     def capture(self):
@@ -381,16 +385,36 @@ class QtipLlama:
     def reset(self):
         self.pos.zero_()
         self.cache_k.zero_(); self.cache_v.zero_()
+        self.steps_done = 0
+
+    def _reserve(self, n_steps):
+        """Refuse on the host what the KV cache cannot hold (the kernels would skip the step and set `status`)."""
+        if self.steps_done + n_steps > self.max_positions:
+            raise RuntimeError(f"{self.steps_done} positions used, {n_steps} more requested: the KV cache holds "
+                               f"{self.max_positions}")
+        self.steps_done += n_steps
+
+    def check_status(self):
+        """Raise if a kernel reported an index outside its buffer (synchronises)."""
+        st = int(self.status.item())
+        if st:
+            raise RuntimeError(f"decode-loop status {st}: 1 = position outside the KV cache, 2 = token outside the "
+                               "embedding table, 4 = token log full")
 
     def feed(self, token_ids):
         """Run the given tokens through the model one position at a time (fills the KV cache); the
         sampled continuation of the last one is left in self.token."""
+        ids = token_ids.tolist()
+        self._reserve(len(ids))
         run = self.graph.replay if self.graph is not None else self.step
-        for t in token_ids.tolist():
+        for t in ids:
+            if not 0 <= int(t) < self.shape.vocab:
+                raise RuntimeError(f"token {t} outside the vocabulary of {self.shape.vocab}")
             self.token.fill_(int(t))
             run()
 
     def generate(self, n_tokens):
+        self._reserve(n_tokens)
         run = self.graph.replay if self.graph is not None else self.step
         for _ in range(n_tokens):
             run()

@@ -29,6 +29,17 @@ def _require_cuda(*tensors):
             raise RuntimeError("qtip_b200 runs on CUDA tensors only (no CPU fallback)")
 
 
+def _check_device(*tensors):
+    """The preallocated-tensor wrappers launch on the CURRENT device and stream (they must stay free of
+    device switches so that a step can be captured into a CUDA graph): refuse tensors that live elsewhere
+    instead of launching a kernel on one GPU with another GPU's pointers."""
+    cur = torch.cuda.current_device()
+    for t in tensors:
+        if t is not None and t.device.index != cur:
+            raise RuntimeError(f"tensor on cuda:{t.device.index} but the current device is cuda:{cur}: "
+                               "call torch.cuda.set_device() / use torch.cuda.device() around qtip_b200 launches")
+
+
 def _dtype_id(t):
     if t.dtype == torch.float16:
         return F16
@@ -239,6 +250,7 @@ def hadamard(x, hadK=None, K=1, transpose=False):
 def rht_fused(x, rows, n, out, *, in_row_stride=None, residual=None, residual_out=None, norm_weight=None, eps=1e-5,
               gate=None, sign_in=None, sign_out=None, hadk_bits=None, kfac=1, transpose=False, scale=1.0):
     """qtip_rht_fused on preallocated tensors (no allocation, graph-capturable); see include/qtip_b200.h."""
+    _check_device(x, out, residual, residual_out, norm_weight, gate, sign_in, sign_out, hadk_bits)
     n_signs = n
     if sign_in is not None:
         n_signs = sign_in.numel()
@@ -275,7 +287,8 @@ def mlp_mid_table(n, device, hadk_bits=None):
             hadk_bits = pack_hadk(get_hadK(n)[0].to(device))
         lib = _lib.load()
         t = torch.zeros(lib.qtip_mlp_mid_table_bytes(), dtype=torch.uint8, device=device)
-        _lib.check(lib.qtip_mlp_mid_prepare(t.data_ptr(), hadk_bits.data_ptr(), int(n), int(k), _stream()), "qtip_mlp_mid_prepare")
+        with torch.cuda.device(t.device):
+            _lib.check(lib.qtip_mlp_mid_prepare(t.data_ptr(), hadk_bits.data_ptr(), int(n), int(k), _stream()), "qtip_mlp_mid_prepare")
         _mid_tables[key] = t
     return t
 
@@ -283,6 +296,7 @@ def mlp_mid_table(n, device, hadk_bits=None):
 def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scale_in, table=None):
     """qtip_mlp_mid: output side of gate/up + SwiGLU + input side of down_proj, one launch.  out: (n) fp16.
     table: mlp_mid_table(n, device); looked up (and built on first use, which allocates) when omitted."""
+    _check_device(out, y_gate, y_up, sign_gate, sign_up, sign_down, table)
     if table is None:
         table = mlp_mid_table(n, out.device)
     st = _lib.load().qtip_mlp_mid(out.data_ptr(), y_gate.data_ptr(), y_up.data_ptr(), sign_gate.data_ptr(), sign_up.data_ptr(),
@@ -294,10 +308,17 @@ def mlp_mid(out, y_gate, y_up, sign_gate, sign_up, sign_down, n, scale_out, scal
     return out
 
 
-def embed_token(res, delta, embed, token):
-    """qtip_embed_token: res = embed[token], delta = 0."""
+def _status_ptr(status):
+    return None if status is None else status.data_ptr()
+
+
+def embed_token(res, delta, embed, token, status=None):
+    """qtip_embed_token: res = embed[token], delta = 0.  A token outside the table leaves res / delta alone and
+    sets bit 2 of `status` (a one-element int32 / uint32 device tensor)."""
+    _check_device(res, delta, embed, token, status)
     _lib.check(_lib.load().qtip_embed_token(res.data_ptr(), delta.data_ptr(), embed.data_ptr(), token.data_ptr(),
-                                            embed.shape[1], _stream()), "qtip_embed_token")
+                                            embed.shape[1], embed.shape[0], _status_ptr(status), _stream()),
+               "qtip_embed_token")
     global launch_count
     launch_count += 1
 
@@ -305,6 +326,7 @@ def embed_token(res, delta, embed, token):
 def lm_head(logits, res, delta, norm_weight, weight, eps):
     """qtip_lm_head: logits = weight @ RMSNorm(res + delta) (fp16 norm semantics of LlamaRMSNorm, fp32 logits)."""
     vocab, hidden = weight.shape
+    _check_device(logits, res, delta, norm_weight, weight)
     _lib.check(_lib.load().qtip_lm_head(logits.data_ptr(), res.data_ptr(), delta.data_ptr(), norm_weight.data_ptr(),
                                         weight.data_ptr(), hidden, vocab, float(eps), _stream()), "qtip_lm_head")
     global launch_count
@@ -312,53 +334,63 @@ def lm_head(logits, res, delta, norm_weight, weight, eps):
     return logits
 
 
-def sample_top_k(token, out_tokens, pos, logits, temperature=0.6, top_k=5, seed=0):
-    """qtip_sample_top_k: next token -> token, out_tokens[pos + 1]; pos += 1 (all on the device)."""
+def sample_top_k(token, out_tokens, pos, logits, temperature=0.6, top_k=5, seed=0, status=None):
+    """qtip_sample_top_k: next token -> token, out_tokens[pos + 1]; pos += 1 (all on the device).  When the token
+    log is full the token is not logged and bit 4 of `status` is set."""
+    _check_device(token, out_tokens, pos, logits, status)
     _lib.check(_lib.load().qtip_sample_top_k(token.data_ptr(), out_tokens.data_ptr(), pos.data_ptr(), logits.data_ptr(),
-                                             logits.numel(), float(temperature), int(top_k), int(seed), _stream()),
+                                             logits.numel(), float(temperature), int(top_k), int(seed),
+                                             out_tokens.numel(), _status_ptr(status), _stream()),
                "qtip_sample_top_k")
     global launch_count
     launch_count += 1
 
 
-def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, theta=10000.0):
+def rope_kv_append(q, k, v, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, theta=10000.0, status=None):
+    """The caches are (max_positions, n_kv_heads*head_dim); a position outside them makes the kernel skip its work
+    and set bit 1 of `status` (same for the three functions below)."""
+    _check_device(q, k, v, cache_k, cache_v, pos, status)
     st = _lib.load().qtip_rope_kv_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
-                                         pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), _stream())
+                                         pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta), cache_k.shape[0],
+                                         _status_ptr(status), _stream())
     _lib.check(st, "qtip_rope_kv_append")
     global launch_count
     launch_count += 1
 
 
 def rope_kv_append_fused(q_out, y_q, y_k, y_v, sign_q, sign_k, sign_v, scale_q, scale_kv, cache_k, cache_v, pos, n_heads,
-                         n_kv_heads, head_dim, theta=10000.0):
+                         n_kv_heads, head_dim, theta=10000.0, status=None):
     """qtip_rope_kv_append_fused: output side of the q/k/v linears + rotary embedding + cache append, one launch."""
+    _check_device(q_out, y_q, y_k, y_v, sign_q, sign_k, sign_v, cache_k, cache_v, pos)
     ptr = lambda t: 0 if t is None else t.data_ptr()   # noqa: E731
     st = _lib.load().qtip_rope_kv_append_fused(q_out.data_ptr(), y_q.data_ptr(), y_k.data_ptr(), y_v.data_ptr(), ptr(sign_q),
                                                ptr(sign_k), ptr(sign_v), float(scale_q), float(scale_kv), cache_k.data_ptr(),
                                                cache_v.data_ptr(), pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta),
-                                               _stream())
+                                               cache_k.shape[0], _status_ptr(status), _stream())
     _lib.check(st, "qtip_rope_kv_append_fused")
     global launch_count
     launch_count += 1
 
 
 def attn_decode_fused(out, y_q, y_k, y_v, sign_q, sign_k, sign_v, scale_q, scale_kv, cache_k, cache_v, pos, n_heads,
-                      n_kv_heads, head_dim, theta=10000.0):
+                      n_kv_heads, head_dim, theta=10000.0, status=None):
     """qtip_attn_decode_fused: output side of q/k/v + rotary + cache append + single-query attention, one launch."""
+    _check_device(out, y_q, y_k, y_v, sign_q, sign_k, sign_v, cache_k, cache_v, pos)
     ptr = lambda t: 0 if t is None else t.data_ptr()   # noqa: E731
     st = _lib.load().qtip_attn_decode_fused(out.data_ptr(), y_q.data_ptr(), y_k.data_ptr(), y_v.data_ptr(), ptr(sign_q),
                                             ptr(sign_k), ptr(sign_v), float(scale_q), float(scale_kv), cache_k.data_ptr(),
                                             cache_v.data_ptr(), pos.data_ptr(), n_heads, n_kv_heads, head_dim, float(theta),
-                                            _stream())
+                                            cache_k.shape[0], _status_ptr(status), _stream())
     _lib.check(st, "qtip_attn_decode_fused")
     global launch_count
     launch_count += 1
     return out
 
 
-def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim):
+def attn_decode(out, q, cache_k, cache_v, pos, n_heads, n_kv_heads, head_dim, status=None):
+    _check_device(out, q, cache_k, cache_v, pos, status)
     st = _lib.load().qtip_attn_decode(out.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(),
-                                      n_heads, n_kv_heads, head_dim, _stream())
+                                      n_heads, n_kv_heads, head_dim, cache_k.shape[0], _status_ptr(status), _stream())
     _lib.check(st, "qtip_attn_decode")
     global launch_count
     launch_count += 1
@@ -374,6 +406,7 @@ def linear_fused(descs, K, m, n, bs=1):
     and peer_max_polls."""
     arr = (_lib.LinearDesc * len(descs))()
     for d, c in zip(descs, arr):
+        _check_device(*(d.get(name) for name in ("y", "codes", "tlut", "x", "workspace", "in_raw", "out", "in_y")))
         for name in ("y", "codes", "tlut", "x", "workspace", "in_raw", "residual", "residual_out", "norm_weight", "gate",
                      "sign_in", "out", "sign_out", "in_y", "in_y_sign"):
             t = d.get(name)

@@ -36,7 +36,9 @@ def _fwht_last_dim(x, scale=1.0):
 
 
 def load_reference(root=None):
-    root = root or os.environ.get("QTIP_REFERENCE_ROOT", "/root/reference")
+    root = root or os.environ.get("QTIP_REFERENCE_ROOT")
+    if not root:
+        raise RuntimeError("set QTIP_REFERENCE_ROOT to a checkout of the upstream QTIP repository")
     if not os.path.isdir(os.path.join(root, "lib", "codebook")):
         raise RuntimeError(f"upstream QTIP tree not found at {root}")
     if "qtip_kernels" not in sys.modules:

@@ -70,7 +70,7 @@ def test_bitshift_linear_forward_golden(golden, mode, K, m, n, rcp):
 
 
 def test_layer4096_vs_upstream_output(golden):
-    """BASELINE configuration 1: 4096x4096, 2 bit, HYB, batch 1 - upstream's CPU forward output is the fixture."""
+    """4096x4096, 2 bit, HYB, batch 1 (upstream's own CPU-runnable case): upstream's CPU forward output is the fixture."""
     g = golden("layer4096")
     lay = synth.make_layer(4096, 4096, 2, seed=1000)
     q = QuantizedLinear(4096, 4096, 16, 16, 16, 2, 2, 9, "quantlut_sym").to(DEV)

@@ -104,7 +104,7 @@ def test_layer_forward_golden(golden, mode, K, m, n, rcp):
 
 
 def test_layer4096_golden(golden):
-    """BASELINE configuration 1 (4096x4096, 2 bit, HYB, batch 1): upstream forward vs both restatements."""
+    """4096x4096, 2 bit, HYB, batch 1 (upstream's own CPU-runnable case): upstream forward vs both restatements."""
     g = golden("layer4096")
     import zlib
     lay = synth.make_layer(4096, 4096, 2, seed=1000)
