@@ -128,15 +128,25 @@ struct SegmentIter {
 };
 
 // Extra destinations of a result row block (tensor parallelism): this rank's slot in every GPU's peer-mapped
-// buffer.  Each value travels as one 8-byte store {value, stamp}; the reader knows a value has arrived when its
-// stamp is the expected sequence number, so no fence, flag or atomic sits between producer and consumers.
+// buffer.  Each value travels as ONE 64-bit scalar store {value in the low word, stamp in the high word}; the reader
+// knows a value has arrived when its stamp is the expected sequence number, so no fence, flag or atomic sits between
+// producer and consumers.  A 64-bit scalar access is single-copy atomic in the PTX memory model (a vector access of
+// two 32-bit elements would not be), so value and stamp can never be observed apart.
 struct OutCopies {
     uint2 *dst[8];
     int n;
 };
 __device__ __forceinline__ void store_stamped(uint2 *p, float v, unsigned stamp) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
+    const unsigned long long q = ((unsigned long long)stamp << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(q) : "memory");
 }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Upper bound on the time one launch spends waiting for the other GPUs' values, whatever the poll limit says.
+constexpr unsigned long long kPeerWaitNs = 200ull * 1000ull * 1000ull;
 
 struct Shared {            // control block at the start of dynamic shared memory
     int is_last;
@@ -338,11 +348,10 @@ __device__ __forceinline__ bool loadE_stamped(const uint2 *p, size_t i, unsigned
     bool ok = true;
 #pragma unroll
     for (int k = 0; k < E; k += 2) {
-        uint4 q;
-        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p + i + k) : "memory");
-        o[k] = __uint_as_float(q.x); o[k + 1] = __uint_as_float(q.z);
-        ok = ok && q.y == want && q.w == want;
+        unsigned long long a, b;   // two 64-bit elements, each {value, stamp} read atomically
+        asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p + i + k) : "memory");
+        o[k] = __uint_as_float((unsigned)a); o[k + 1] = __uint_as_float((unsigned)b);
+        ok = ok && (unsigned)(a >> 32) == want && (unsigned)(b >> 32) == want;
     }
     return ok;
 }
@@ -350,14 +359,18 @@ __device__ __forceinline__ bool loadE_stamped(const uint2 *p, size_t i, unsigned
 // Before the whole CTA reads the vectors, one warp watches 32 sample elements of each until they are current:
 // the other 31 warps stay off the memory system while the data is still on its way (150 000 threads re-reading
 // with system scope slow the arriving stores down by orders of magnitude).  Bounded like the reads themselves.
-__device__ __forceinline__ void await_samples(const PeerIn &peer, int n, unsigned want) {
-    if (threadIdx.x < 32) {
+__device__ __forceinline__ void await_samples(const PeerIn &peer, int n, unsigned want, unsigned long long t_start,
+                                              bool dead) {
+    // `dead` may differ between threads (another CTA can set the status word at any time): the warp agrees on it,
+    // and the CTA barrier below is reached by every thread whatever it saw
+    if (threadIdx.x < 32 && !__any_sync(kFullMask, dead)) {
         const size_t idx = (size_t)threadIdx.x * (n >> 5);
         for (int p = 0; p < peer.n; p++) {
             for (unsigned polls = 0; polls < peer.max_polls; polls++) {
-                uint2 q;
-                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(peer.y[p] + idx) : "memory");
-                if (__all_sync(kFullMask, q.y == want)) break;
+                unsigned long long q;
+                asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(q) : "l"(peer.y[p] + idx) : "memory");
+                if (__all_sync(kFullMask, (unsigned)(q >> 32) == want)) break;
+                if (globaltimer_ns() - t_start > kPeerWaitNs) break;
                 __nanosleep(200);
             }
         }
@@ -381,9 +394,15 @@ __device__ __forceinline__ void fused_input_regs(const FusedIn &I, const PeerIn 
     // all operand vectors are requested before any is used
     if (use_peers) {
         const unsigned want = *reinterpret_cast<const volatile unsigned *>(peer.seq);
-        await_samples(peer, n, want);
+        // A wait that ran out in an EARLIER launch (a lost or desynchronised GPU) leaves *status set: every later
+        // launch then reads once and goes on instead of spinning again, so a dead peer costs one bounded wait in
+        // total, not one per launch.  The host reads the word and stops or falls back.
+        const bool dead = *reinterpret_cast<const volatile unsigned *>(peer.status) != 0u;
+        const unsigned long long t_start = globaltimer_ns();
+        await_samples(peer, n, want, t_start, dead);
         // A warp reads, checks and - for stragglers - retries as a unit: the loop is uniform over the warp (vote), so
-        // no lane ever spins on its own while its warp waits for it, and it ends after max_polls rounds at the latest.
+        // no lane ever spins on its own while its warp waits for it, and it ends after max_polls rounds or
+        // kPeerWaitNs at the latest.
         bool ok;
         for (unsigned round = 0;; round++) {
             ok = loadE_stamped<E>(peer.y[0], jA, want, v);
@@ -393,7 +412,8 @@ __device__ __forceinline__ void fused_input_regs(const FusedIn &I, const PeerIn 
 #pragma unroll
                 for (int k = 0; k < E; k++) v[k] += t[k];
             }
-            if (__all_sync(kFullMask, ok) || round >= peer.max_polls) break;
+            if (__all_sync(kFullMask, ok || dead) || round >= peer.max_polls) break;
+            if (__any_sync(kFullMask, globaltimer_ns() - t_start > kPeerWaitNs)) break;
             __nanosleep(200);
         }
         if (!ok) atomicOr(peer.status, 1u);

@@ -88,3 +88,32 @@ def test_torch_ops_register_with_fake_impl():
     with FakeTensorMode():
         y = op(torch.empty(4096 * 11008 // 256, 32, dtype=torch.int16), torch.empty(1, 11008), torch.empty(512, 2, dtype=torch.float16))
         assert y.shape == (1, 4096) and y.dtype == torch.float32
+
+
+def test_wrappers_refuse_tensors_of_another_device(monkeypatch):
+    """The preallocated-tensor wrappers launch on the current device: a tensor that lives on another GPU must be
+    refused on the host, before any launch (no GPU needed: the device query is faked)."""
+    import types
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 1)
+    on0 = types.SimpleNamespace(device=types.SimpleNamespace(index=0))
+    on1 = types.SimpleNamespace(device=types.SimpleNamespace(index=1))
+    ops._check_device(on1, None, on1)
+    with pytest.raises(RuntimeError, match="current device"):
+        ops._check_device(on1, on0)
+    for fn, args in ((ops.embed_token, (on0, on0, on0, on0)), (ops.lm_head, (on0, on0, on0, on0, types.SimpleNamespace(
+            device=on0.device, shape=(8, 8)), 1e-5)), (ops.attn_decode, (on0, on0, on0, on0, on0, 1, 1, 128)),
+                     (ops.rope_kv_append, (on0, on0, on0, on0, on0, on0, 1, 1, 128))):
+        with pytest.raises(RuntimeError, match="current device"):
+            fn(*args)
+
+
+def test_decode_model_refuses_more_positions_than_the_cache_holds():
+    """QtipLlama.feed / generate count positions on the host and raise before a step would index past the caches."""
+    from qtip_b200.llama import QtipLlama
+    m = QtipLlama.__new__(QtipLlama)          # host bookkeeping only: no device buffers
+    m.max_positions, m.steps_done = 10, 0
+    m._reserve(6)
+    m._reserve(4)
+    with pytest.raises(RuntimeError, match="KV cache holds 10"):
+        m._reserve(1)
+    assert m.steps_done == 10
