@@ -8,11 +8,13 @@
 //            row-block boundaries: perfectly balanced bytes, but row blocks shared by several
 //            CTAs need the ticket reduction below.
 //
-// Data path.  Inside a segment warp w takes blocks w, w+32, ...  A lane pulls its 4K contiguous
-// bytes of a block with one streaming (L1-bypassing) 64/96/128-bit load straight into registers;
-// each warp keeps D such loads in flight (software pipeline across its blocks and across segment
-// boundaries), which is 32 KiB in flight per SM.  The wrap-around bits of the tail-biting stream
-// come from lane+1 by shuffle.  A lane decodes its 16 trellis states into four mma.m16n8k16 A
+// Data path.  Inside a segment warp w owns a CONTIGUOUS run of blocks (1/32 of the segment).  It pulls the
+// run in chunks of up to 1 KiB with one bulk copy (cp.async.bulk, the 1-D form of TMA) per chunk into a
+// two-slot ring of its own in shared memory, completion on an mbarrier of its own; the next chunk -
+// of this or of the following segment - is always in flight while one is decoded (up to 64 KiB in
+// flight per SM, no registers held, no load-latency stalls in the loop).  A lane reads its 4K bytes of a
+// block and those of lane+1 (the wrap-around bits of the tail-biting stream) from the ring, so the loop
+// has no shuffles.  A lane decodes its 16 trellis states into four mma.m16n8k16 A
 // fragments in registers - HYB: h = s*(s+1), entry (h>>6)&1023 of a 1024-entry table (the 512-entry
 // LUT and its sign-flipped twin) kept as 32 lane-private copies in shared memory, so gathers never
 // conflict - and multiplies them with x held in the B fragment (column j of B = batch row j, so up
@@ -20,9 +22,9 @@
 // in shared memory in fragment order (one 16-byte load per block and lane).
 //
 // The kernel is instruction-issue bound, not HBM bound (about 5 instructions per state are
-// irreducible: shift, multiply-add hash, mask, multiply-add address, shared load), so the loop
-// carries no barriers: an earlier variant that staged the codes through a cp.async.bulk ring with
-// mbarriers spent 74 of 158 instructions per block on ring control and ran 35 % slower.
+// irreducible: shift, multiply-add hash, mask, multiply-add address, shared load; the integer pipes
+// run at half rate on this part).  The ring costs about one instruction per block because it is
+// private to a warp: no producer warp, no CTA barrier, one bounded mbarrier wait per chunk.
 //
 // Reduction.  Warps of a CTA are summed through shared memory at the end of a segment.  When a
 // row block is shared by several CTAs each stores its partial sums to the workspace and takes a
@@ -32,8 +34,9 @@
 // Launch overlap.  The kernel is launched with programmatic stream serialization: everything that
 // touches only weights (the first code loads, the table build) runs before griddepcontrol.wait,
 // i.e. while the previous kernel of the stream drains; x, out and the workspace are touched only
-// after it.  The single-GPU kernel contains no spin-waits; the tensor-parallel instantiation (TP) has one bounded
-// wait, for the other GPUs' result values (see PeerIn below).
+// after it.  Waits: the per-chunk mbarrier wait (bounded; a time-out sets word 1 of the workspace's control
+// area and the kernel runs to its end with meaningless results) and, in the tensor-parallel instantiation
+// (TP), one bounded wait for the other GPUs' result values (see PeerIn below).
 //
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
 #include <mutex>
@@ -48,13 +51,17 @@ constexpr int kConsumerWarps = 32;
 // sign flip is needed) x 32 lane-private copies x half2 = 128 KiB.  Entry e, copy l at byte e*128 + l*4:
 // every lane reads its own bank, so a warp's 32 random lookups never conflict.
 constexpr int kLutBytes = 1024 * 32 * 4;
-constexpr int kCtrlBytes = 256;
+constexpr int kCtrlBytes = 1024;      // Shared (256 bytes) + two mbarriers per warp
+constexpr int kBarOffset = 256;
+constexpr int kMaxChunkBytes = 1024;  // bytes of packed codes per bulk copy
+constexpr unsigned kRingSpinLimit = 1u << 22;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxBatch = 8;
 
 // ---- workspace layout (all offsets fixed, independent of the problem) -----------------------------
 // [0, 64 KiB)   ticket counters, one uint32 per 32-row block (m <= 524288); zero between calls
 // [64 KiB, +256) word 0: counter of finished CTAs (fused output transform); zero between calls
+//               word 1: sticky flag, set if a wait for a bulk copy ever ran out (never cleared by the kernels)
 // [.., end)     partial sums: [row block][contributor][8 batch x 32 rows] fp32
 constexpr size_t kCounterBytes = 64 * 1024;
 constexpr size_t kPartialOffset = kCounterBytes + 256;
@@ -333,13 +340,42 @@ struct MatvecBatch {
     MatvecProblem p[kMaxProblems];
 };
 
-// Next lane's codes (wrap-around bits of the tail-biting stream: lane 31 takes lane 0's).
+// ---- per-warp staging ring ----------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// One bulk copy global -> shared (addresses and size multiples of 16 bytes), completion counted on `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// A lane's 4K bytes of a block in the ring (address = block start + lane * 4K); every access pattern below is
+// conflict-free (8 / 16 bytes per lane contiguous, or words at stride 3).
 template <int K>
-__device__ __forceinline__ LaneCodes<K> next_lane_codes(const LaneCodes<K> &c, int lane) {
-    LaneCodes<K> o;
-#pragma unroll
-    for (int i = 0; i < K; i++) o.w[i] = __shfl_sync(kFullMask, c.w[i], lane + 1);
-    return o;
+__device__ __forceinline__ LaneCodes<K> lds_lane_codes(uint32_t addr) {
+    LaneCodes<K> c;
+    if constexpr (K == 2) {
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(c.w[0]), "=r"(c.w[1]) : "r"(addr));
+    } else if constexpr (K == 3) {
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(c.w[0]) : "r"(addr));
+        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(c.w[1]) : "r"(addr));
+        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(c.w[2]) : "r"(addr));
+    } else {
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c.w[0]), "=r"(c.w[1]), "=r"(c.w[2]), "=r"(c.w[3]) : "r"(addr));
+    }
+    return c;
 }
 
 // E consecutive stamped values of one GPU's partial vector, read once; false if a stamp is not `want`
@@ -486,21 +522,27 @@ __device__ __forceinline__ void fused_output_regs(const FusedOut &O, const float
 
 // XS: x is staged once per CTA in shared memory, permuted so that a lane's four B-fragment words of
 // a block are one 16-byte load; otherwise they are read from global memory (L1-resident) per block.
-// DB: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
-// D:  software-pipeline depth - each warp keeps D of its blocks' codes in flight in registers.
+// db: the cross-warp reduction buffer is double-buffered, which drops one CTA barrier per segment.
 // blockIdx.y selects the problem of the batch (all problems have the same m, n, K, bs).
 // TP: the tensor-parallel fields (PeerIn / Signal) are live; the single-GPU instantiation carries none of that code.
-// NW: decoding warps per CTA.  32 (64 registers per thread) for launches with fused sides, whose register transforms
-// are written for 1024 threads; 16 (up to 128 registers, twice the blocks in flight per warp) for plain launches:
-// the same bytes in flight per SM with more instruction-level parallelism per warp, ~10 % faster on large matrices.
-template <int K, bool XS, bool DB, int D, bool TP, int NW>
+// NW: warps per CTA (32: the register transforms of the fused sides are written for 1024 threads).
+// C:  blocks per bulk copy; xs_offset: byte offset of the staged x in shared memory (the host fits the ring, the
+// reduction buffers, x and the scratch of the fused input side into 227 KiB and picks C accordingly).
+template <int K, bool XS, bool TP, int NW, int C>
 __global__ void __launch_bounds__(NW * 32, 1)
-    matvec_hyb_kernel(const __grid_constant__ MatvecBatch batch, int m, int n, int bs, int kmax, int mode) {
+    matvec_hyb_kernel(const __grid_constant__ MatvecBatch batch, int m, int n, int bs, int kmax, int mode, int db,
+                      int xs_offset) {
     constexpr int kBlockBytes = 128 * K;
+    constexpr int chunk_blocks = C;
+    const bool DB = db != 0;
     constexpr int kConsumerWarps = NW, kThreads = NW * 32;     // shadow the file-scope defaults
+    constexpr int kWarpShift = NW == 32 ? 5 : 4;
+    static_assert(NW == 32 || NW == 16, "a segment is split over 16 or 32 warps");
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: control block | LUT | reduction buffer(s) [NW][bs][32] fp32 | x (bs, n) fp16 permuted |
-    //         fp32 scratch of the fused input transform (n values, padded)
+    // layout: control block (incl. two mbarriers per warp) | LUT | ring slot 0 [NW][chunk] | ring slot 1 [NW][chunk] |
+    //         reduction buffer(s) [NW][bs][32] fp32 | (padding) | x (bs, n) fp16 permuted
+    // The fp32 scratch of the fused input transform overlays ring slot 1 and what follows it up to x: slot 1 is
+    // first filled after the transform is done.
     const MatvecProblem &P = batch.p[blockIdx.y];
     float *__restrict__ out = P.out;
     const uint8_t *__restrict__ codes = P.codes;
@@ -508,10 +550,13 @@ __global__ void __launch_bounds__(NW * 32, 1)
     const uint32_t *__restrict__ tlut = P.tlut;
     Shared *sh = reinterpret_cast<Shared *>(smem);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kCtrlBytes);
+    const int slot_bytes = chunk_blocks * kBlockBytes;             // per warp
+    uint8_t *ring = smem + kCtrlBytes + kLutBytes;
     const int red_floats = kConsumerWarps * 32 * bs;
-    float *red = reinterpret_cast<float *>(smem + kCtrlBytes + kLutBytes);
-    uint4 *xs = reinterpret_cast<uint4 *>(red + (DB ? 2 : 1) * red_floats);
-    float *fscratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xs) + (size_t)bs * n * 2);
+    float *red = reinterpret_cast<float *>(ring + 2 * NW * slot_bytes);
+    (void)chunk_blocks;
+    uint4 *xs = reinterpret_cast<uint4 *>(smem + xs_offset);
+    float *fscratch = reinterpret_cast<float *>(ring + NW * slot_bytes);
 
     unsigned *counters = reinterpret_cast<unsigned *>(P.workspace);
     unsigned *done_counter = reinterpret_cast<unsigned *>(P.workspace + kCounterBytes);
@@ -520,34 +565,73 @@ __global__ void __launch_bounds__(NW * 32, 1)
     const int nb = n >> 5, mb = m >> 5;
     const int G = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint8_t *lane_codes = codes + lane * (4 * K);
 
-    // Segment bookkeeping in 32-bit block indices (B = mb*nb < 2^31 is checked by the host).
-    // rows mode: segments are whole row blocks c, c+G, ...; stream-K: [r0, r1) cut at row boundaries.
+    // Segment bookkeeping in 32-bit block indices (B = mb*nb < 2^30 is checked by the host).
+    // rows mode: segments are whole row blocks c, c+G, ...; stream-K: [r0, r1) cut at row boundaries.  Both are
+    // "the part of row block M from pos up to min(end, (M+1)*nb), then on to row block M + mstep at seg_end + gap",
+    // so the loops below carry no mode branches and no divisions.
     const int B = mb * nb;
-    int pos, end;
-    if (mode == kModeRows) { pos = blockIdx.x * nb; end = B; }
-    else { pos = (int)range_start(blockIdx.x, B, G); end = (int)range_start(blockIdx.x + 1, B, G); }
-    auto seg_end_of = [&](int p) { return mode == kModeRows ? p + nb : min(end, (p / nb + 1) * nb); };
-    auto next_seg = [&](int e) { return mode == kModeRows ? e + (G - 1) * nb : e; };
-
-    // First loads of this warp: packed codes are weights, so they are issued before the table build
-    // and before waiting for the previous kernel of the stream.
-    LaneCodes<K> buf[D];
-    int seg_end = seg_end_of(pos);
-    {
-#pragma unroll
-        for (int d = 0; d < D; d++) {
-            const int b = pos + warp + d * kConsumerWarps;
-            if (b < seg_end) buf[d] = load_lane_codes<K>(lane_codes + (size_t)b * kBlockBytes);
-        }
+    int pos, end, M, mstep, gap;
+    if (mode == kModeRows) { pos = blockIdx.x * nb; end = B; M = blockIdx.x; mstep = G; gap = (G - 1) * nb; }
+    else {
+        pos = (int)range_start(blockIdx.x, B, G); end = (int)range_start(blockIdx.x + 1, B, G);
+        M = pos / nb; mstep = 1; gap = 0;
     }
+    // warp w's run of a segment [p, e): an even split of its blocks, contiguous in memory
+    auto run_of = [&](int p, int e, int &r0, int &r1) {
+        const int cnt = e - p;
+        r0 = p + ((warp * cnt) >> kWarpShift);
+        r1 = p + (((warp + 1) * cnt) >> kWarpShift);
+    };
+    int seg_end = min(end, (M + 1) * nb);
+
+    // The ring of this warp: slot s at ring + (s*NW + warp)*slot_bytes, its barrier at bar_w + 8s.
+    const uint32_t ring_w = smem_u32(ring) + warp * slot_bytes;
+    const uint32_t slot_stride = NW * slot_bytes;
+    const uint32_t bar_w = smem_u32(smem + kBarOffset) + warp * 16;
+    if (lane == 0) { mbar_init(bar_w, 1); mbar_init(bar_w + 8, 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    // Issue cursor: walks this warp's chunks (over all segments of the CTA, in order) one or two chunks ahead of
+    // the decoding; uniform over the warp, lane 0 issues the copy.
+    int i_M = M, i_seg_end = seg_end, i_blk = 0, i_run_end = 0;
+    bool i_valid = pos < end;
+    unsigned ichunk = 0;
+    if (i_valid) run_of(pos, i_seg_end, i_blk, i_run_end);
+    auto issue = [&]() {
+        while (i_valid && i_blk >= i_run_end) {
+            const int i_pos = i_seg_end + gap;
+            i_M += mstep;
+            if (i_pos >= end) { i_valid = false; break; }
+            i_seg_end = min(end, (i_M + 1) * nb);
+            run_of(i_pos, i_seg_end, i_blk, i_run_end);
+        }
+        if (!i_valid) return;
+        const int nblk = min(chunk_blocks, i_run_end - i_blk);
+        if (lane == 0)
+            bulk_load(ring_w + (ichunk & 1u) * slot_stride, codes + (size_t)i_blk * kBlockBytes, (uint32_t)(nblk * kBlockBytes),
+                      bar_w + (ichunk & 1u) * 8);
+        i_blk += nblk;
+        ichunk++;
+    };
+    // First chunk of this warp: packed codes are weights, so the copy starts before the table build and before
+    // waiting for the previous kernel of the stream.
+    issue();
     if (threadIdx.x == 0) sh->is_last = 0;
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
-    // flips the sign of the first (low) half of the pair
-    for (int i = threadIdx.x; i < 1024 * 8; i += kThreads) {
-        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
-        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+    // flips the sign of the first (low) half of the pair.  Thread t writes the 16-byte groups t, t + kThreads, ...:
+    // the LUT words it needs are requested first, then stored.
+    {
+        constexpr int kGroupsPerThread = 1024 * 8 / kThreads;     // 8 (or 16)
+        uint32_t tl[kGroupsPerThread / 2];
+#pragma unroll
+        for (int j = 0; j < kGroupsPerThread / 2; j++) tl[j] = __ldg(tlut + (((threadIdx.x + kThreads * j) >> 3) & 511));
+#pragma unroll
+        for (int j = 0; j < kGroupsPerThread; j++) {
+            // group i = t + kThreads*j: entry (i >> 3) & 511, sign bit i >> 12 (= j / (kGroupsPerThread/2))
+            const uint32_t e = tl[j % (kGroupsPerThread / 2)] ^ ((uint32_t)(j / (kGroupsPerThread / 2)) << 15);
+            reinterpret_cast<uint4 *>(lut)[threadIdx.x + kThreads * j] = make_uint4(e, e, e, e);
+        }
     }
     grid_launch_dependents();  // the next kernel of the stream may start its own weight-only prologue
     grid_dependency_wait();    // x, out and the workspace belong to the stream's data flow
@@ -562,15 +646,71 @@ __global__ void __launch_bounds__(NW * 32, 1)
             // A thread owns 8 consecutive values; the loads of all operand vectors are issued together so
             // the whole prologue costs one L2 round trip, not one per array.
             const FusedIn &I = P.in;
+#ifndef QTIP_PROLOGUE_SMEM
             if (NW == 32 && n == 4096) fused_input_regs<4, TP>(I, P.peer, n, xs, fscratch, sh->warp_sums);
             else if (NW == 32 && n == 8192) fused_input_regs<8, TP>(I, P.peer, n, xs, fscratch, sh->warp_sums);
-            else {
+            else
+#endif
+            {
             const int nvec = n >> 3;
+            int p = 0;
+            while ((1 << p) < n) p++;
+            const bool use_peers = TP && P.peer.n > 0;
+            const bool deferred = I.y_prev != nullptr || use_peers;
+            if (deferred) {
+                // the producer's raw result (or the sum of the GPUs' partial results) -> scratch -> transform; its
+                // sign, scale and fp16 rounding are applied when the values are picked up below
+                if (use_peers) {
+                    const unsigned want = *reinterpret_cast<const volatile unsigned *>(P.peer.seq);
+                    const bool dead = *reinterpret_cast<const volatile unsigned *>(P.peer.status) != 0u;
+                    const unsigned long long t_start = globaltimer_ns();
+                    await_samples(P.peer, n, want, t_start, dead);
+                    for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {      // trip counts are uniform per warp
+                        const size_t j = (size_t)vi * 8;
+                        float v[8];
+                        bool ok;
+                        for (unsigned round = 0;; round++) {
+                            ok = loadE_stamped<8>(P.peer.y[0], j, want, v);
+                            for (int q = 1; q < P.peer.n; q++) {
+                                float t8[8];
+                                ok = loadE_stamped<8>(P.peer.y[q], j, want, t8) && ok;
+#pragma unroll
+                                for (int k = 0; k < 8; k++) v[k] += t8[k];
+                            }
+                            if (__all_sync(kFullMask, ok || dead) || round >= P.peer.max_polls) break;
+                            if (__any_sync(kFullMask, globaltimer_ns() - t_start > kPeerWaitNs)) break;
+                            __nanosleep(200);
+                        }
+                        if (!ok) atomicOr(P.peer.status, 1u);
+#pragma unroll
+                        for (int k = 0; k < 8; k++) fscratch[pad((int)j + k)] = v[k];
+                    }
+                } else {
+                    for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
+                        const size_t j = (size_t)vi * 8;
+                        float v[8];
+                        loadE_f32<8>(I.y_prev, j, v, true);
+#pragma unroll
+                        for (int k = 0; k < 8; k++) fscratch[pad((int)j + k)] = v[k];
+                    }
+                }
+                __syncthreads();
+                fwht_shared(fscratch, n, p);
+            }
             float ss = 0.f;
             for (int vi = threadIdx.x; vi < nvec; vi += kThreads) {
                 const size_t j = (size_t)vi * 8;
                 float v[8], rs[8], gt[8], sg[8];
-                load8_f16(I.x_raw, j, v);
+                if (deferred) {
+                    float ps[8];
+                    if (I.prev_sign) load8_f32(I.prev_sign, j, ps);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        float y = fscratch[pad((int)j + k)] * I.prev_scale;
+                        if (I.prev_sign) y *= ps[k];
+                        v[k] = __half2float(__float2half_rn(y));      // the producer's output is an fp16 tensor
+                    }
+                } else load8_f16(I.x_raw, j, v);
                 if (I.residual) load8_f16(I.residual, j, rs);
                 if (I.gate && !I.norm_weight) load8_f16(I.gate, j, gt);
                 if (I.sign_in && !I.norm_weight) load8_f16(I.sign_in, j, sg);
@@ -610,8 +750,6 @@ __global__ void __launch_bounds__(NW * 32, 1)
                 }
             }
             __syncthreads();
-            int p = 0;
-            while ((1 << p) < n) p++;
             fwht_shared(fscratch, n, p);
             for (int i = threadIdx.x; i < (n >> 1); i += kThreads) {
                 const int blk = i >> 4, w = i & 15;
@@ -635,67 +773,66 @@ __global__ void __launch_bounds__(NW * 32, 1)
         }
     }
     __syncthreads();
+    issue();   // second chunk: ring slot 1 (the scratch of the fused input side lay over it until the barrier above)
 
     const int g = lane >> 2, t = lane & 3;
     const int xg = g < bs ? g : 0;  // lanes of unused batch columns alias row 0; their results are never stored
     const uint32_t *xrow = reinterpret_cast<const uint32_t *>(x + (size_t)xg * n + 2 * t);
-    const uint4 *xsrow = xs + (size_t)xg * nb * 4 + t;
+    const uint32_t xsrow = smem_u32(xs) + (uint32_t)(xg * nb * 4 + t) * 16u;   // shared-memory address of this lane's fragments
     const uint32_t lut_lane = smem_u32(lut) + lane * 4;
+    const uint32_t own_off = lane * (4 * K), nxt_off = ((lane + 1) & 31) * (4 * K);   // lane 31 wraps to lane 0: tail-biting
 
     uint32_t segno = 0;
+    unsigned cchunk = 0;       // chunks consumed so far: slot cchunk & 1, barrier phase (cchunk >> 1) & 1
+    bool ring_dead = false;    // a wait ran out: stop waiting (the results are meaningless, the kernel terminates)
     while (pos < end) {
-        const int M = pos / nb;
-        const int first = pos - M * nb + warp;      // this warp's first block inside the row block
-        const int count = seg_end - pos;            // blocks in the segment
+        int r0, r1;
+        run_of(pos, seg_end, r0, r1);
+        const int row0 = M * nb;
         float acc[2][4] = {};
-        // warp handles blocks first, first+32, ... ; buf[d] holds block i*... in round-robin order
-        const uint8_t *src = lane_codes + (size_t)(pos + warp) * kBlockBytes;
-        int i = warp;
-        for (; i + (D - 1) * kConsumerWarps < count; i += D * kConsumerWarps) {
-            // all D buffered blocks are valid in this trip
-#pragma unroll
-            for (int d = 0; d < D; d++) {
-                const LaneCodes<K> own = buf[d];
-                const int nxt_i = i + (d + D) * kConsumerWarps;
-                if (nxt_i < count) buf[d] = load_lane_codes<K>(src + (size_t)(d + D) * kConsumerWarps * kBlockBytes);
-                const LaneCodes<K> nxt = next_lane_codes<K>(own, lane);
-                uint32_t xb[4];
-                const int N = first + (i - warp) + d * kConsumerWarps;
-                if constexpr (XS) { const uint4 a = xsrow[N * 4]; xb[0] = a.x; xb[1] = a.y; xb[2] = a.z; xb[3] = a.w; }
-                else { const uint32_t *xp = xrow + 16 * N; xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12); }
-                decode_block<K>(own, nxt, xb, acc, lut_lane);
+        uint32_t xsp = xsrow + (uint32_t)(r0 - row0) * 64u;    // x fragments of the block being decoded (64 bytes per block)
+        const uint32_t *xgp = xrow + 16 * (r0 - row0);
+        for (int blk = r0; blk < r1; blk += C) {
+            const int nblk = min(C, r1 - blk);
+            const uint32_t slot = ring_w + (cchunk & 1u) * slot_stride;
+            if (!ring_dead) {
+                const uint32_t bar = bar_w + (cchunk & 1u) * 8, parity = (cchunk >> 1) & 1u;
+                unsigned spins = 0;
+                while (!mbar_try_wait(bar, parity)) {
+                    if (++spins > kRingSpinLimit) {
+                        ring_dead = true;
+                        if (lane == 0) atomicOr(done_counter + 1, 1u);
+                        break;
+                    }
+                }
             }
-            src += (size_t)D * kConsumerWarps * kBlockBytes;
-        }
-        // tail: fewer than D blocks left for this warp (no further loads in this segment)
 #pragma unroll
-        for (int d = 0; d < D; d++) {
-            if (i + d * kConsumerWarps < count) {
-                const LaneCodes<K> own = buf[d];
-                const LaneCodes<K> nxt = next_lane_codes<K>(own, lane);
-                uint32_t xb[4];
-                const int N = first + (i - warp) + d * kConsumerWarps;
-                if constexpr (XS) { const uint4 a = xsrow[N * 4]; xb[0] = a.x; xb[1] = a.y; xb[2] = a.z; xb[3] = a.w; }
-                else { const uint32_t *xp = xrow + 16 * N; xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12); }
-                decode_block<K>(own, nxt, xb, acc, lut_lane);
+            for (int i = 0; i < C; i++) {
+                if (i < nblk) {
+                    const LaneCodes<K> own = lds_lane_codes<K>(slot + i * kBlockBytes + own_off);
+                    const LaneCodes<K> nxt = lds_lane_codes<K>(slot + i * kBlockBytes + nxt_off);
+                    uint32_t xb[4];
+                    if constexpr (XS) {
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xb[0]), "=r"(xb[1]), "=r"(xb[2]), "=r"(xb[3]) : "r"(xsp + i * 64));
+                    }
+                    else { const uint32_t *xp = xgp + 16 * i; xb[0] = __ldg(xp); xb[1] = __ldg(xp + 4); xb[2] = __ldg(xp + 8); xb[3] = __ldg(xp + 12); }
+                    decode_block<K>(own, nxt, xb, acc, lut_lane);
+                }
             }
+            if constexpr (XS) xsp += C * 64;
+            else xgp += C * 16;
+            __syncwarp();      // every lane has read the slot before it is filled again
+            issue();
+            cchunk++;
         }
-        // next segment: start its first loads before the CTA-wide reduction of this one
-        const int npos = next_seg(seg_end);
-        int nseg_end = seg_end;
-        if (npos < end) {
-            nseg_end = seg_end_of(npos);
-#pragma unroll
-            for (int d = 0; d < D; d++) {
-                const int b = npos + warp + d * kConsumerWarps;
-                if (b < nseg_end) buf[d] = load_lane_codes<K>(lane_codes + (size_t)b * kBlockBytes);
-            }
-        }
+        // a segment that covers its whole row block has no other contributor (true for every segment in rows mode)
+        const bool whole = pos == row0 && seg_end - pos == nb;
         finish_segment<kConsumerWarps>(acc, DB ? red + (segno & 1) * red_floats : red, sh, out, partial, counters, M, nb,
-                                       (long)B, G, kmax, m, bs, mode == kModeRows, !DB, TP ? P.sig.copies : OutCopies{}, stamp);
+                                       (long)B, G, kmax, m, bs, whole, !DB, TP ? P.sig.copies : OutCopies{}, stamp);
         segno++;
-        pos = npos;
-        seg_end = nseg_end;
+        pos = seg_end + gap;
+        M += mstep;
+        seg_end = min(end, (M + 1) * nb);
     }
 
     if (TP && P.sig.seq) {
@@ -849,62 +986,100 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
     return QTIP_OK;
 }
 
-template <int K, bool XS, bool DB, bool TP, int NW>
-int launch_hyb_variant_tp(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
-    constexpr int D = (K == 2 ? 4 : 2) * (32 / NW);  // blocks in flight per warp: NW warps x D x 128K bytes = 32 KiB per SM
+struct SmemPlan {
+    int chunk_blocks, xs_offset, total, db;
+};
+
+template <int K, bool XS, bool TP, int NW, int C>
+int launch_hyb_variant_tp(const MatvecBatch &batch, int nprob, int m, int n, int bs, const SmemPlan &plan, cudaStream_t s) {
     static bool attr_set[64] = {};
+    static std::mutex attr_mutex;
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, DB, D, TP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kSmemLimit));
-        attr_set[dev] = true;
+    if (dev < 0 || dev >= 64) return QTIP_ERR_BAD_ARG;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        if (!attr_set[dev]) {
+            QTIP_CUDA_TRY(cudaFuncSetAttribute(matvec_hyb_kernel<K, XS, TP, NW, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               kSmemLimit));
+            attr_set[dev] = true;
+        }
     }
     const Partition p = make_partition(m, n, K, nprob);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid, nprob);
     cfg.blockDim = dim3(NW * 32);
-    cfg.dynamicSmemBytes = smem_total;
+    cfg.dynamicSmemBytes = plan.total;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, DB, D, TP, NW>, batch, m, n, bs, p.kmax, p.mode));
+    QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, TP, NW, C>, batch, m, n, bs, p.kmax, p.mode, plan.db,
+                                     plan.xs_offset));
     return check_launch();
 }
 
-template <int K, bool XS, bool DB>
-int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs, int smem_total, cudaStream_t s) {
-    bool tp = false, fused = false;
+template <int K, bool XS, int C>
+int launch_hyb_variant_c(const MatvecBatch &batch, int nprob, int m, int n, int bs, const SmemPlan &plan, cudaStream_t s) {
+    bool tp = false;
     for (int i = 0; i < nprob; i++) {
         const MatvecProblem &q = batch.p[i];
         tp = tp || q.peer.n > 0 || q.sig.seq != nullptr;
-        fused = fused || q.in.x_raw || q.in.y_prev || q.ep.final;
     }
-    if (tp) return launch_hyb_variant_tp<K, XS, DB, true, 32>(batch, nprob, m, n, bs, smem_total, s);
-    if (fused) return launch_hyb_variant_tp<K, XS, DB, false, 32>(batch, nprob, m, n, bs, smem_total, s);
-    return launch_hyb_variant_tp<K, XS, DB, false, 16>(batch, nprob, m, n, bs, smem_total, s);
+    if (tp) return launch_hyb_variant_tp<K, XS, true, 32, C>(batch, nprob, m, n, bs, plan, s);
+    return launch_hyb_variant_tp<K, XS, false, 32, C>(batch, nprob, m, n, bs, plan, s);
+}
+
+template <int K, bool XS>
+int launch_hyb_variant(const MatvecBatch &batch, int nprob, int m, int n, int bs, const SmemPlan &plan, cudaStream_t s) {
+    constexpr int kMaxC = kMaxChunkBytes / (128 * K);      // 4 for K = 2, 2 for K = 3 and 4
+    if constexpr (kMaxC >= 4) {
+        if (plan.chunk_blocks >= 4) return launch_hyb_variant_c<K, XS, 4>(batch, nprob, m, n, bs, plan, s);
+    }
+    if (plan.chunk_blocks >= 2) return launch_hyb_variant_c<K, XS, 2>(batch, nprob, m, n, bs, plan, s);
+    return launch_hyb_variant_c<K, XS, 1>(batch, nprob, m, n, bs, plan, s);
+}
+
+// Fit ring, reduction buffer(s), x and the scratch of the fused input side into the shared memory left beside
+// the table.  Returns false if not even a one-block ring fits.
+template <int K>
+bool plan_smem(int n, int bs, bool xs, bool db, bool fused_in, SmemPlan &plan) {
+    constexpr int NW = kConsumerWarps, BB = 128 * K;
+    const int red_bytes = (db ? 2 : 1) * NW * 32 * bs * (int)sizeof(float);
+    const int x_bytes = xs ? bs * n * 2 : 0;
+    // fwht_shared wants n + n/32 + 8 floats, fwht_regs 32 rows of n/32 + 4
+    const int scratch_bytes = fused_in ? (n + (n >> 5) + 136) * (int)sizeof(float) : 0;
+    const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
+    plan.db = db ? 1 : 0;
+    for (int c = kMaxChunkBytes / BB; c >= 1; c >>= 1) {          // 4, 2, 1: the instantiated chunk sizes
+        const int slot = NW * c * BB;                                   // one ring slot, all warps
+        const int after_slot1 = slot + red_bytes;                       // bytes from slot 1 up to x
+        const int pad = scratch_bytes > after_slot1 ? scratch_bytes - after_slot1 : 0;
+        const int total = 2 * slot + red_bytes + pad + x_bytes;
+        if (total <= avail) {
+            plan.chunk_blocks = c;
+            plan.xs_offset = kCtrlBytes + kLutBytes + 2 * slot + red_bytes + pad;
+            plan.total = kCtrlBytes + kLutBytes + total;
+            return true;
+        }
+    }
+    return false;
 }
 
 // fused_in: the batch uses the fused input transform (needs x staged in shared memory plus fp32 scratch)
 template <int K>
 int launch_hyb_batch(const MatvecBatch &batch, int nprob, int m, int n, int bs, bool fused_in, cudaStream_t s) {
-    // shared memory: control + table are fixed; then the reduction buffer(s) and, when it fits, x
-    const int red_bytes = kConsumerWarps * 32 * bs * (int)sizeof(float);
-    const int x_bytes = bs * n * 2;
-    const int scratch_bytes = fused_in ? (n + (n >> 5) + 8) * (int)sizeof(float) : 0;
-    const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
-    const bool db = 2 * red_bytes <= avail / 2;
-    const int fixed = (db ? 2 : 1) * red_bytes;
-    const bool xs = fixed + x_bytes + scratch_bytes <= avail;
-    if (fused_in && !xs) return QTIP_ERR_BAD_SHAPE;
-    const int smem_total = kCtrlBytes + kLutBytes + fixed + (xs ? x_bytes + scratch_bytes : 0);
-    if (xs && db) return launch_hyb_variant<K, true, true>(batch, nprob, m, n, bs, smem_total, s);
-    if (xs) return launch_hyb_variant<K, true, false>(batch, nprob, m, n, bs, smem_total, s);
-    if (db) return launch_hyb_variant<K, false, true>(batch, nprob, m, n, bs, smem_total, s);
-    return launch_hyb_variant<K, false, false>(batch, nprob, m, n, bs, smem_total, s);
+    // shared memory: control + table are fixed; then the ring, the reduction buffer(s) and, when it fits, x.
+    // Preference: x staged and double-buffered reduction; then give up the second reduction buffer; then x.
+    SmemPlan plan;
+    if (plan_smem<K>(n, bs, true, true, fused_in, plan)) return launch_hyb_variant<K, true>(batch, nprob, m, n, bs, plan, s);
+    if (plan_smem<K>(n, bs, true, false, fused_in, plan)) return launch_hyb_variant<K, true>(batch, nprob, m, n, bs, plan, s);
+    if (fused_in) return QTIP_ERR_BAD_SHAPE;      // the fused input side leaves x in shared memory
+    if (plan_smem<K>(n, bs, false, true, false, plan)) return launch_hyb_variant<K, false>(batch, nprob, m, n, bs, plan, s);
+    if (plan_smem<K>(n, bs, false, false, false, plan)) return launch_hyb_variant<K, false>(batch, nprob, m, n, bs, plan, s);
+    return QTIP_ERR_BAD_SHAPE;
 }
 
 template <int K>
