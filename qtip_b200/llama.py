@@ -52,13 +52,24 @@ class _Linear:
     ("col": rows of the full matrix, "row": columns, None: not sharded).  Codes and LUT come from the local
     generator, the sign vectors from the shared one (all ranks draw the full vectors and keep their slice)."""
 
-    def __init__(self, m, n, K, g_local, g_shared, device, split=None, rank=0, tp=1):
+    def __init__(self, m, n, K, g_local, g_shared, device, split=None, rank=0, tp=1, shard_full=False):
         self.m, self.n, self.K = m, n, K
-        self.codes = torch.randint(0, 65536, (m * n // 256, 16 * K), generator=g_local, device=device,
-                                   dtype=torch.int32).to(torch.int16)
-        self.tlut = torch.randn(512, 2, generator=g_shared, device=device).half()
         n_full = n * tp if split == "row" else n
         m_full = m * tp if split == "col" else m
+        if shard_full:
+            # the FULL matrix from the shared generator (same on every rank, and the same as a tp = 1 model draws),
+            # then this rank's shard of it: the ranks together hold exactly one unsharded model
+            full = torch.randint(0, 65536, (m_full * n_full // 256, 16 * K), generator=g_shared, device=device,
+                                 dtype=torch.int32).to(torch.int16)
+            if split == "col":
+                full = tp_mod.shard_column_parallel(full, None, torch.zeros(m_full), m_full, n_full, K, rank, tp)[0]
+            elif split == "row":
+                full = tp_mod.shard_row_parallel(full, torch.zeros(n_full), None, m_full, n_full, K, rank, tp)[0]
+            self.codes = full.contiguous()
+        else:
+            self.codes = torch.randint(0, 65536, (m * n // 256, 16 * K), generator=g_local, device=device,
+                                       dtype=torch.int32).to(torch.int16)
+        self.tlut = torch.randn(512, 2, generator=g_shared, device=device).half()
         SU = (torch.randn(n_full, generator=g_shared, device=device).sign() + 1e-5).sign().half()
         # SV carries the weight scale; keep the layer's output variance about that of its input
         SV = (torch.randn(m_full, generator=g_shared, device=device).sign() + 1e-5).sign().float() / math.sqrt(n_full)
@@ -70,9 +81,12 @@ class _Linear:
 class QtipLlama:
 
     def __init__(self, shape=LLAMA2_7B, max_positions=512, device="cuda:0", seed=3000, tp_rank=0, tp_size=1,
-                 group=None):
+                 group=None, full_model_shards=False):
         """tp_size > 1: this process holds rank tp_rank's shards (qtip_b200.tp) and `group` is the
-        torch.distributed group of the tp_size ranks (one all-reduce after o_proj and after down_proj)."""
+        torch.distributed group of the tp_size ranks (one all-reduce after o_proj and after down_proj).
+        full_model_shards: every rank draws the full matrices (from the shared generator) and keeps its shard, so
+        that the ranks together hold the one model a tp_size = 1 instance with the same seed holds; the default
+        draws each rank's shard directly (same distribution, much faster for large shapes)."""
         self.shape, self.device, self.max_positions = shape, torch.device(device), max_positions
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         s, dev, tp = shape, self.device, tp_size
@@ -86,8 +100,8 @@ class QtipLlama:
         for d in (s.hidden, H, KV, MLP):
             assert d % 32 == 0, f"width {d} is not a multiple of 32"
         assert s.head_dim == 128, "the decode attention kernel is built for head_dim 128"
-        col = dict(split="col" if tp > 1 else None, rank=tp_rank, tp=tp)
-        row = dict(split="row" if tp > 1 else None, rank=tp_rank, tp=tp)
+        col = dict(split="col" if tp > 1 else None, rank=tp_rank, tp=tp, shard_full=full_model_shards)
+        row = dict(split="row" if tp > 1 else None, rank=tp_rank, tp=tp, shard_full=full_model_shards)
         self.layers = []
         for _ in range(s.n_layers):
             L = dict(q=_Linear(H, s.hidden, s.K, gl, g, dev, **col), k=_Linear(KV, s.hidden, s.K, gl, g, dev, **col),

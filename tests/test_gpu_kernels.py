@@ -199,6 +199,19 @@ def test_decompress_gemm(K, m, n, bs):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("K,m,n,bs", [(2, 1024, 2048, 16), (4, 256, 256, 40)])
+def test_decompress_gemm_vs_oracle(K, m, n, bs):
+    """The tensor-core path directly against the CPU oracle (decode of the kernel layout + dense product), with no
+    CUDA kernel of this library on the reference side."""
+    lay = synth.make_layer(m, n, K, seed=3400 + K, bs=bs)
+    y = ops.decompress_gemm(dev(lay["codes"]), dev(lay["x"]), dev(lay["tlut"]), K, m, n)
+    torch.cuda.synchronize()
+    want = C.matvec_dense(C.decode_kernel(lay["codes"], m, n, K, lay["tlut"]), lay["x"])
+    assert ops.gemm_status(DEV) == 0
+    assert rel_l2(y.cpu().numpy(), want) < 1e-5
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("ctx", [1, 7, 200, 257, 2048, 2049, 5000])
 @pytest.mark.parametrize("heads", [(8, 8), (16, 2)])
 def test_attn_decode_matches_fp32_softmax(ctx, heads):

@@ -18,6 +18,6 @@ def test_peer_sum_matches_all_reduce(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(29530 + world), os.path.join(HERE, "tp_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=280, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "tp_worker ok" in r.stdout

@@ -1,15 +1,20 @@
 """Worker of test_gpu_tp.py: one tensor-parallel rank (launched by torch.distributed.run, one process per GPU).
 
-Decodes a fixed token sequence twice with the same sharded model - once with the partial results of o_proj /
-down_proj summed inside the consuming launch through peer-mapped memory, once with an NCCL all-reduce between the
-launches - and checks that the logits agree and that no bounded wait ran out."""
+The ranks hold the shards of ONE unsharded model (QtipLlama(full_model_shards=True)).  The worker decodes a fixed
+token sequence twice - once with the partial results of o_proj / down_proj summed inside the consuming launch
+through peer-mapped memory, once with an NCCL all-reduce between the launches - and checks that the logits agree,
+that no bounded wait ran out, and (rank 0) that they equal the CPU oracle's evaluation of the unsharded buffers in
+the tensor-parallel parametrisation (per-chunk Hadamard transforms, lib/codebook/bitshift.py:437-441, 465-469
+upstream)."""
 import os
 import sys
 
 import torch
 import torch.distributed as dist
 
-sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+HERE = os.path.dirname(os.path.abspath(__file__))
+for p_ in (os.path.join(HERE, ".."), os.path.join(HERE, "..", "oracle"), HERE):
+    sys.path.insert(0, p_)
 from qtip_b200.llama import LlamaShape, QtipLlama  # noqa: E402
 
 
@@ -19,7 +24,8 @@ def main():
     dev = f"cuda:{local}"
     dist.init_process_group("nccl", device_id=torch.device(dev))
     shape = LlamaShape(n_layers=3, hidden=4096, n_heads=32, n_kv_heads=32, head_dim=128, mlp=11008, vocab=4096, K=2)
-    model = QtipLlama(shape, max_positions=32, device=dev, seed=3000, tp_rank=rank, tp_size=world, group=dist.group.WORLD)
+    model = QtipLlama(shape, max_positions=32, device=dev, seed=3000, tp_rank=rank, tp_size=world, group=dist.group.WORLD,
+                      full_model_shards=True)
     assert model.peers is not None, "peer-memory path not active"
     tokens = torch.tensor([5, 17, 99, 1234, 7, 4000])
 
@@ -52,10 +58,32 @@ def main():
     ref = fused_eager.clone()
     dist.broadcast(ref, 0)
     assert torch.equal(ref, fused_eager), "ranks disagree"
+    # the sharded model against the CPU oracle's evaluation of the unsharded buffers (rank 0; the others wait)
+    oerr = 0.0
+    if rank == 0:
+        import numpy as np
+        import c_oracle
+        from model_oracle import oracle_logits
+        c_oracle.build()
+        full = QtipLlama(shape, max_positions=8, device=dev, seed=3000, tp_rank=0, tp_size=1, full_model_shards=True)
+        n_tok = 3
+        want = oracle_logits(full, tokens[:n_tok].tolist(), tp=world)
+        got = fused_eager[n_tok - 1].float().cpu().numpy().reshape(-1)
+        oerr = float(np.linalg.norm(got - want.reshape(-1)) / np.linalg.norm(want))
+        assert oerr < 5e-3, f"tensor-parallel logits differ from the oracle: rel l2 {oerr}"
+        del full
+    # the other ranks wait on the host (the store), not inside a collective kernel, while rank 0 runs the CPU oracle
+    import datetime
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 0:
+        store.set("oracle_done", "1")
+    else:
+        store.wait(["oracle_done"], datetime.timedelta(seconds=900))
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
-        print(f"tp_worker ok: world {world}, peer-sum vs all-reduce max rel diff {err:.2e}")
+        print(f"tp_worker ok: world {world}, peer-sum vs all-reduce max rel diff {err:.2e}, vs CPU oracle (unsharded buffers, "
+              f"per-chunk transforms) rel l2 {oerr:.2e}")
 
 
 if __name__ == "__main__":
