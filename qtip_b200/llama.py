@@ -78,15 +78,23 @@ class _Linear:
         self.SV32 = (self.SV * 32).contiguous()
 
 
+class _LinearView:
+    """Sign / scale slices of one chunk (q, k, v, gate or up) of a fused matrix."""
+
+
 class QtipLlama:
 
     def __init__(self, shape=LLAMA2_7B, max_positions=512, device="cuda:0", seed=3000, tp_rank=0, tp_size=1,
-                 group=None, full_model_shards=False):
+                 group=None, full_model_shards=False, fuse_qkv=False):
         """tp_size > 1: this process holds rank tp_rank's shards (qtip_b200.tp) and `group` is the
         torch.distributed group of the tp_size ranks (one all-reduce after o_proj and after down_proj).
         full_model_shards: every rank draws the full matrices (from the shared generator) and keeps its shard, so
         that the ranks together hold the one model a tp_size = 1 instance with the same seed holds; the default
-        draws each rank's shard directly (same distribution, much faster for large shapes)."""
+        draws each rank's shard directly (same distribution, much faster for large shapes).
+        fuse_qkv: q||k||v and gate||up are ONE QTIP matrix each (out_features H + 2*KV and 2*MLP: 12288 x 4096 and
+        22016 x 4096 at the 7B shape, the layers upstream's published decode speed was measured with, README.md:31,
+        48-51): one packed matrix, one LUT, one SU, and the output-side transform per q / k / v (gate / up) chunk,
+        i.e. upstream's rcp = 2 layout with 3 (2) chunks (lib/codebook/bitshift.py:465-469).  Single GPU only."""
         self.shape, self.device, self.max_positions = shape, torch.device(device), max_positions
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         s, dev, tp = shape, self.device, tp_size
@@ -102,17 +110,31 @@ class QtipLlama:
         assert s.head_dim == 128, "the decode attention kernel is built for head_dim 128"
         col = dict(split="col" if tp > 1 else None, rank=tp_rank, tp=tp, shard_full=full_model_shards)
         row = dict(split="row" if tp > 1 else None, rank=tp_rank, tp=tp, shard_full=full_model_shards)
+        self.fuse_qkv = bool(fuse_qkv)
+        assert not (self.fuse_qkv and tp > 1), "fused q||k||v / gate||up matrices are built for a single GPU"
+        self.linear_names = ("qkv", "o", "gu", "down") if self.fuse_qkv else ("q", "k", "v", "o", "gate", "up", "down")
         self.layers = []
         for _ in range(s.n_layers):
-            L = dict(q=_Linear(H, s.hidden, s.K, gl, g, dev, **col), k=_Linear(KV, s.hidden, s.K, gl, g, dev, **col),
-                     v=_Linear(KV, s.hidden, s.K, gl, g, dev, **col), o=_Linear(s.hidden, H, s.K, gl, g, dev, **row),
-                     gate=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col), up=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col),
-                     down=_Linear(s.hidden, MLP, s.K, gl, g, dev, **row))
+            if self.fuse_qkv:
+                L = dict(qkv=_Linear(H + 2 * KV, s.hidden, s.K, gl, g, dev), o=_Linear(s.hidden, H, s.K, gl, g, dev),
+                         gu=_Linear(2 * MLP, s.hidden, s.K, gl, g, dev), down=_Linear(s.hidden, MLP, s.K, gl, g, dev))
+                # the chunks of the fused matrices as the rest of the step sees them: sign / scale slices only
+                for name, lin, lo, hi in (("q", L["qkv"], 0, H), ("k", L["qkv"], H, H + KV), ("v", L["qkv"], H + KV, H + 2 * KV),
+                                          ("gate", L["gu"], 0, MLP), ("up", L["gu"], MLP, 2 * MLP)):
+                    view = _LinearView()
+                    view.SU, view.SV, view.SV32 = lin.SU, lin.SV[lo:hi], lin.SV32[lo:hi]
+                    L[name] = view
+            else:
+                L = dict(q=_Linear(H, s.hidden, s.K, gl, g, dev, **col), k=_Linear(KV, s.hidden, s.K, gl, g, dev, **col),
+                         v=_Linear(KV, s.hidden, s.K, gl, g, dev, **col), o=_Linear(s.hidden, H, s.K, gl, g, dev, **row),
+                         gate=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col), up=_Linear(MLP, s.hidden, s.K, gl, g, dev, **col),
+                         down=_Linear(s.hidden, MLP, s.K, gl, g, dev, **row))
             L["ln1"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
             L["ln2"] = (1 + 0.02 * torch.randn(s.hidden, generator=g, device=dev)).half()
             # sign vectors of launches that share one input, concatenated
-            L["SU_qkv"] = torch.cat([L["q"].SU, L["k"].SU, L["v"].SU]).contiguous()
-            L["SU_gu"] = torch.cat([L["gate"].SU, L["up"].SU]).contiguous()
+            if not self.fuse_qkv:
+                L["SU_qkv"] = torch.cat([L["q"].SU, L["k"].SU, L["v"].SU]).contiguous()
+                L["SU_gu"] = torch.cat([L["gate"].SU, L["up"].SU]).contiguous()
             L["SV_gu"] = torch.cat([L["gate"].SV32, L["up"].SV32]).contiguous()
             self.layers.append(L)
         self.embed = (0.02 * torch.randn(s.vocab, s.hidden, generator=g, device=dev)).half()
@@ -152,7 +174,8 @@ class QtipLlama:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.steps_done = 0   # host-side count of positions consumed since reset()
         need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, 1)
-                   for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
+                   for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden),
+                                  (H + 2 * KV, s.hidden), (2 * MLP, s.hidden)))
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
         self.workspaces = [self.workspace] + [torch.zeros(need, dtype=torch.uint8, device=dev) for _ in range(2)]
         pow2 = lambda d: d & (d - 1) == 0  # noqa: E731
@@ -184,6 +207,9 @@ class QtipLlama:
         # gate/up output side + SwiGLU + down input side as one cluster launch (widths with a Hadamard factor)
         self.mid_fused = (not self.fuse_out_m) and (not self.fuse_in_m) and ops.mlp_mid_supported(MLP)
         self.mid_table = ops.mlp_mid_table(MLP, dev, self.bits[self.kf_m]) if self.mid_fused else None
+        if self.fuse_qkv:
+            assert self.fuse_in_h and (self.attn_fused or self.defer_qkv), \
+                "fused q||k||v / gate||up matrices need the in-kernel input transform and a deferred q/k/v output side"
         if self.peers is not None:
             import torch.distributed as dist
             torch.cuda.synchronize(dev)
@@ -243,7 +269,11 @@ class QtipLlama:
             if self.fuse_in_h and (self.attn_fused or self.defer_qkv or (self.fuse_out_hl and self.fuse_out_kv)):
                 dq = self.defer_qkv or self.attn_fused
                 fin = dict(delta_src, residual=res_a, residual_out=res_b, norm_weight=L["ln1"], in_scale=inv_h / 32)
-                if H == KV:
+                if self.fuse_qkv:
+                    assert dq, "the fused q||k||v matrix needs its output side inside the attention / rotary launch"
+                    self._linears([L["qkv"]], None, [self.y_qkv], s.hidden, H + 2 * KV,
+                                  fused_in=dict(fin, sign_ins=[L["qkv"].SU]))
+                elif H == KV:
                     self._linears([L["q"], L["k"], L["v"]], None, [y_q, y_k, y_v], s.hidden, H,
                                   fused_in=dict(fin, sign_ins=[L["q"].SU, L["k"].SU, L["v"].SU]), outs=None if dq else [q, k, v],
                                   sign_outs=[L["q"].SV32, L["k"].SV32, L["v"].SV32], out_scale=inv_hl)
@@ -314,10 +344,13 @@ class QtipLlama:
             if self.fuse_in_h:
                 fin = dict(delta_src, residual=res_b, residual_out=res_a, norm_weight=L["ln2"], in_scale=inv_h / 32,
                            sign_ins=[L["gate"].SU, L["up"].SU])
-                fo = self.fuse_out_m
-                self._linears([L["gate"], L["up"]], None, [y_g, y_u], s.hidden, MLP, fused_in=fin,
-                              outs=[self.gu[:MLP], self.gu[MLP:]] if fo else None,
-                              sign_outs=[L["gate"].SV32, L["up"].SV32], out_scale=inv_m)
+                fo = self.fuse_out_m and not self.fuse_qkv
+                if self.fuse_qkv:
+                    self._linears([L["gu"]], None, [self.y_gu], s.hidden, 2 * MLP, fused_in=dict(fin, sign_ins=[L["gu"].SU]))
+                else:
+                    self._linears([L["gate"], L["up"]], None, [y_g, y_u], s.hidden, MLP, fused_in=fin,
+                                  outs=[self.gu[:MLP], self.gu[MLP:]] if fo else None,
+                                  sign_outs=[L["gate"].SV32, L["up"].SV32], out_scale=inv_m)
             else:
                 fo = False
                 xg = self.xh_gu

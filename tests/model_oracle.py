@@ -29,6 +29,14 @@ def oracle_logits(model, tokens, tp=1):
                             rcp=rcp if tp > 1 else 0, tp=tp)
         return f16(y.reshape(-1))
 
+    def lin_chunks(l, v, chunks):
+        """A fused matrix (q||k||v or gate||up): one input side, the output-side transform per chunk of out_features
+        (upstream's rcp = 2 layout with `chunks` chunks)."""
+        y = C.layer_forward(v.astype(np.float32), l.codes.cpu().numpy().view(np.uint16), l.m, l.n, l.K,
+                            l.tlut.cpu().numpy(), l.SU.float().cpu().numpy(), l.SV.cpu().numpy(), hadk(l.n),
+                            hadk(l.m // chunks), rcp=2, tp=chunks)
+        return np.split(f16(y.reshape(-1)), chunks)
+
     COL, ROW = (2, 1) if tp > 1 else (0, 0)
 
     def norm(v, w):
@@ -51,7 +59,11 @@ def oracle_logits(model, tokens, tp=1):
 
         for li, L in enumerate(model.layers):
             h = norm(x, L["ln1"])
-            q, k, v = rope(lin(L["q"], h, COL)), rope(lin(L["k"], h, COL)), lin(L["v"], h, COL).reshape(-1, s.head_dim)
+            if "qkv" in L:
+                q, k, v = lin_chunks(L["qkv"], h, 3)
+            else:
+                q, k, v = lin(L["q"], h, COL), lin(L["k"], h, COL), lin(L["v"], h, COL)
+            q, k, v = rope(q), rope(k), v.reshape(-1, s.head_dim)
             ks[li].append(k); vs[li].append(v)
             Kc, Vc = np.stack(ks[li], 1).astype(np.float64), np.stack(vs[li], 1).astype(np.float64)   # (heads, ctx, hd)
             sc = np.einsum("hd,hcd->hc", q.astype(np.float64), Kc) / math.sqrt(s.head_dim)
@@ -60,7 +72,7 @@ def oracle_logits(model, tokens, tp=1):
             att = f16(np.einsum("hc,hcd->hd", p, Vc).reshape(-1))
             x = f16(x + lin(L["o"], att, ROW))
             h = norm(x, L["ln2"])
-            g, u = lin(L["gate"], h, COL), lin(L["up"], h, COL)
+            g, u = lin_chunks(L["gu"], h, 2) if "gu" in L else (lin(L["gate"], h, COL), lin(L["up"], h, COL))
             act = f16(f16(g / (1.0 + np.exp(-g))) * u)
             x = f16(x + lin(L["down"], act, ROW))
         h = norm(x, model.ln_f)

@@ -118,12 +118,14 @@ def test_graph_replay_matches_eager():
 # ---------------------------------------------------------------------------------------------------------
 # the benchmarked launch graph (register transforms, deferred output sides, fused attention, MLP middle) vs the oracle
 # ---------------------------------------------------------------------------------------------------------
-def test_decode_step_at_the_benchmarked_shape_matches_the_oracle():
+@pytest.mark.parametrize("fuse_qkv", [False, True])
+def test_decode_step_at_the_benchmarked_shape_matches_the_oracle(fuse_qkv):
     """hidden 4096 / 32 heads / MLP 11008: the shape whose decode graph the benchmark times.  Here the input
     transforms run in registers inside the matvec launches, the output sides of o_proj / down_proj are deferred into
-    the next launch, attention runs fused with the q/k/v output sides and the MLP middle is the cluster kernel."""
+    the next launch, attention runs fused with the q/k/v output sides and the MLP middle is the cluster kernel.
+    fuse_qkv: q||k||v and gate||up as one 12288 x 4096 and one 22016 x 4096 matrix (upstream's fused layers)."""
     shape = LlamaShape(n_layers=2, hidden=4096, n_heads=32, n_kv_heads=32, head_dim=128, mlp=11008, vocab=2048, K=2)
-    model = QtipLlama(shape, max_positions=8, device=DEV, seed=21)
+    model = QtipLlama(shape, max_positions=8, device=DEV, seed=21, fuse_qkv=fuse_qkv)
     assert model.defer_h and model.attn_fused and model.mid_fused and model.fuse_in_h and model.fuse_in_hl
     tokens = [7, 1999, 345]
     model.reset()
