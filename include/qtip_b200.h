@@ -90,6 +90,13 @@ int qtip_decompress_matvec(float *out, const void *codes, const void *x, const v
 int qtip_decompress_gemm(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n, int bs,
                          unsigned *status, void *stream);
 
+/* qtip_decompress_gemm for the compute codes: 3INST / 1MAD, V = 1, plain layout (no LUT).  The batched form of
+ * BitshiftLinear.forward's dense branch for codes without a matvec kernel upstream (lib/codebook/bitshift.py:454-463:
+ * unpack_trellis + get_hatW + matmul), again without materialising the matrix; the decoded weights are the ones
+ * qtip_decode_plain produces (1MAD: the fp32 value rounded once to fp16).  Same shape and status rules. */
+int qtip_decompress_gemm_plain(float *out, const void *codes, const void *x, int code, int K, int m, int n, int bs,
+                               unsigned *status, void *stream);
+
 /* One to four QTIP linears of the same shape in ONE launch (e.g. q/k/v, or gate/up), each optionally with
  * its input-side and output-side transforms fused into the matvec kernel, i.e. the whole of
  * BitshiftLinear.forward (lib/codebook/bitshift.py:428-472) for a decode step in one kernel:

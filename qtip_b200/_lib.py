@@ -36,6 +36,7 @@ SIGNATURES = {
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_decompress_matvec_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "qtip_decompress_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "qtip_decompress_gemm_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "qtip_linear_fused": (_i, [ctypes.POINTER(LinearDesc), _i, _i, _i, _i, _i, _vp]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),

@@ -102,7 +102,12 @@ class BitshiftLinear(nn.Module):
                      kfac=K_left or 1, transpose=True, scale=1.0 / (math.sqrt(seg_n) * self.scale),
                      out_dtype=torch.float16).reshape(bs, n)
 
-        if bs <= ops.MAX_MATVEC_BATCH:
+        v1 = self.cb.code in (ops.CODE_3INST, ops.CODE_1MAD)
+        if v1 and ops.gemm_plain_supported(m, n, bs):
+            # compute codes: the tensor-core kernel decodes eight states per 44-bit window and is the faster one at
+            # every batch size it takes (it needs whole 128 x 64 tiles)
+            y = ops.decompress_gemm_plain(trellis, xh, self.cb.code, self.cb.K, m, n)
+        elif bs <= ops.MAX_MATVEC_BATCH:
             if self.has_kernel:
                 y = ops.decompress_matvec(trellis, xh, self.cb.tlut, self.cb.K, m, n, workspace=self.workspace)
             else:

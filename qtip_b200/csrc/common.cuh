@@ -61,6 +61,18 @@ __device__ __forceinline__ __half decode_1mad(uint32_t s16) {
     return __float2half_rn(__fdiv_rn((float)y, 147.800537109375f));
 }
 
+// The same value from a table over the 1021 possible byte sums (built with decode_1mad's own arithmetic, so it is
+// bit-identical): one shared-memory load instead of a convert, an IEEE divide and a second convert.
+constexpr int kMadTableEntries = 1024;
+__device__ __forceinline__ void build_1mad_table(__half *tab) {
+    for (int i = threadIdx.x; i < kMadTableEntries; i += blockDim.x)
+        tab[i] = __float2half_rn(__fdiv_rn((float)(i - 510), 147.800537109375f));
+}
+__device__ __forceinline__ __half decode_1mad_tab(uint32_t s16, const __half *tab) {
+    const uint32_t x = s16 * 34038481u + 76625530u;
+    return tab[__vsadu4(x, 0u)];
+}
+
 // Streaming (read-once) global loads of packed codes: keep them out of L1.
 __device__ __forceinline__ uint32_t ld_stream_u32(const void *p) {
     uint32_t v;

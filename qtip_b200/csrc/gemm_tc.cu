@@ -14,6 +14,9 @@
 //   * warps 0-3 read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 = rows) and
 //     write out (coalesced along rows); with a 2-way column split the two CTAs of a row range add
 //     into a zeroed output (two addends: order-independent, so still deterministic).
+// The compute codes (3INST / 1MAD, V = 1, plain layout) use the same kernel with another producer: a lane decodes
+// eight consecutive states of a tile row (44 stream bits) and stores the eight weights as ONE 16-byte chunk of the
+// swizzled A tile; no table is built.  That path is bound by the per-weight arithmetic, not by the tensor pipe.
 // This replaces decode-to-HBM + dense GEMM of BitshiftLinearKernelAG upstream
 // (lib/codebook/bitshift.py:476-489), which writes and re-reads 16x the packed bytes at 2 bits.
 //
@@ -23,6 +26,8 @@
 // Every mbarrier wait is bounded: after kSpinLimit polls the waiter records an error code in
 // `status`, raises a CTA-wide abort flag that makes every later wait fall through, and the kernel
 // still runs to its end, frees its tensor memory and returns (with meaningless results).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace qtip {
@@ -65,15 +70,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned *status,
+// false: the wait gave up (its own limit, or another waiter raised the abort flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned *status,
                                           unsigned code) {
-    if (mbar_try_wait(bar, parity)) return;
+    if (mbar_try_wait(bar, parity)) return true;
     for (unsigned spin = 0; spin < kSpinLimit; spin++) {
-        if (mbar_try_wait(bar, parity)) return;
-        if (*abort_flag) return;
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0u, code);
+    return false;
+}
+// bounded wait that does not look at the abort flag (used before tensor memory is released)
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (unsigned spin = 0; spin < kSpinLimit; spin++)
+        if (mbar_try_wait(bar, parity)) return;
 }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -99,12 +111,26 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-template <int K>
+// 48 stream bits of a plain-layout tile starting at bit pos (circular over the tile's 16K words), first bit at bit 47
+__device__ __forceinline__ uint64_t plain_bits48(const uint16_t *__restrict__ words, int nwords, int pos) {
+    int w = pos >> 4;
+    uint64_t v = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int wi = w + i;
+        if (wi >= nwords) wi -= nwords;
+        v = (v << 16) | __ldg(words + wi);
+    }
+    return (v << (pos & 15)) >> 16;
+}
+
+template <int K, int CODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     decompress_gemm_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
                            const uint32_t *__restrict__ tlut, int m, int n, int bs, int npad, int splitk,
                            unsigned *__restrict__ status) {
     constexpr int kBlockBytes = 128 * K;
+    constexpr bool kHyb = CODE == QTIP_CODE_HYB;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
@@ -137,9 +163,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     // lane-private copies of the table: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit of
     // the hash flips the first weight of the pair, so it is folded into the table (no per-state sign op)
-    for (int i = threadIdx.x; i < 1024 * 8; i += kGemmThreads) {
-        const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
-        reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+    __half *mad_tab = reinterpret_cast<__half *>(lut);     // 1MAD: byte sum -> weight (the table area is otherwise unused)
+    if constexpr (CODE == QTIP_CODE_1MAD) build_1mad_table(mad_tab);
+    if constexpr (kHyb) {
+        for (int i = threadIdx.x; i < 1024 * 8; i += kGemmThreads) {
+            const uint32_t e = __ldg(tlut + ((i >> 3) & 511)) ^ ((uint32_t)(i >> 12) << 15);
+            reinterpret_cast<uint4 *>(lut)[i] = make_uint4(e, e, e, e);
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -171,10 +201,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (brow >= bs) return make_uint4(0u, 0u, 0u, 0u);
             return *reinterpret_cast<const uint4 *>(x + (size_t)brow * n + c0 + step * kStageCols + c * 8);
         };
-        LaneCodes<K> own_next;
+        LaneCodes<K> own_next = {};
         uint4 xv0_next = make_uint4(0u, 0u, 0u, 0u), xv1_next = xv0_next;
+        // plain layout (V = 1 codes): tile (tile row, tile column) = 16K words at ((row/16)*(n/16) + col/16)*16K; this
+        // lane decodes row pr of each of the warp's four tiles, columns 8*ph .. 8*ph+7
+        const uint16_t *pcodes = reinterpret_cast<const uint16_t *>(codes);
+        const int tn = n >> 4, pr = lane >> 1, ph = lane & 1;
         if (group < nsteps) {
-            own_next = load_lane_codes<K>(src + (size_t)group * 2 * kBlockBytes);
+            if constexpr (kHyb) own_next = load_lane_codes<K>(src + (size_t)group * 2 * kBlockBytes);
             if (has0) xv0_next = load_x(group, tid8);
             if (has1) xv1_next = load_x(group, tid8 + 256);
         }
@@ -183,14 +217,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const LaneCodes<K> own = own_next;
             const uint4 xv0 = xv0_next, xv1 = xv1_next;
             if (step + kGroups < nsteps) {
-                own_next = load_lane_codes<K>(src + (size_t)(step + kGroups) * 2 * kBlockBytes);
+                if constexpr (kHyb) own_next = load_lane_codes<K>(src + (size_t)(step + kGroups) * 2 * kBlockBytes);
                 if (has0) xv0_next = load_x(step + kGroups, tid8);
                 if (has1) xv1_next = load_x(step + kGroups, tid8 + 256);
             }
-            if (round > 0) mbar_wait(smem_addr(&ctl->empty[s]), (round - 1) & 1, abort_flag, status, 1u);
-            LaneCodes<K> nxt;
+            // V = 1: the 44 bits this lane needs of each of its four tiles are requested before the wait for the stage
+            uint64_t pbits[4];
+            if constexpr (!kHyb) {
 #pragma unroll
-            for (int i = 0; i < K; i++) nxt.w[i] = __shfl_sync(kFullMask, own.w[i], lane + 1);
+                for (int tt = 0; tt < 4; tt++) {
+                    const int ks = tt >> 1, ms = tt & 1;
+                    const size_t tile = (size_t)(r0 / 16 + 2 * rb + ms) * tn + (size_t)((c0 + step * kStageCols) / 16 + 2 * cb + ks);
+                    pbits[tt] = plain_bits48(pcodes + tile * (16 * K), 16 * K, (pr * 16 + ph * 8) * K);
+                }
+            }
+            if (round > 0) mbar_wait(smem_addr(&ctl->empty[s]), (round - 1) & 1, abort_flag, status, 1u);
+            LaneCodes<K> nxt = {};
+            if constexpr (kHyb) {
+#pragma unroll
+                for (int i = 0; i < K; i++) nxt.w[i] = __shfl_sync(kFullMask, own.w[i], lane + 1);
+            }
             // B tile: rows = batch (zero beyond bs), 64 columns of x, 16-byte chunks swizzled by row % 8
             const uint32_t bst = b_base + s * b_stage_bytes;
             if (has0) {
@@ -203,21 +249,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const uint32_t dst = bst + brow * 128 + ((c ^ (brow & 7)) << 4);
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(xv1.x), "r"(xv1.y), "r"(xv1.z), "r"(xv1.w) : "memory");
             }
-            const uint32_t ast = a_base + s * kAStageBytes + row_off;
+            if constexpr (kHyb) {
+                const uint32_t ast = a_base + s * kAStageBytes + row_off;
 #pragma unroll
-            for (int tt = 0; tt < 4; tt++) {
-                const int ks = tt >> 1, ms = tt & 1;
-                uint32_t st[4];
-                lane_states<K>(lane_slice<K>(own, tt), lane_slice<K>(nxt, tt), st);
+                for (int tt = 0; tt < 4; tt++) {
+                    const int ks = tt >> 1, ms = tt & 1;
+                    uint32_t st[4];
+                    lane_states<K>(lane_slice<K>(own, tt), lane_slice<K>(nxt, tt), st);
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int c = q >> 1, d = q & 1;
-                    const uint32_t h = hyb_hash(st[q]);
-                    uint32_t w;
-                    asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0xFFC0u) << 1)));
-                    const uint32_t chunk = (uint32_t)(4 * cb + 2 * ks + c);
-                    const uint32_t dst = ast + (uint32_t)(2 * ms + d) * 1024u + ((chunk ^ (uint32_t)a) << 4);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(w) : "memory");
+                    for (int q = 0; q < 4; q++) {
+                        const int c = q >> 1, d = q & 1;
+                        const uint32_t h = hyb_hash(st[q]);
+                        uint32_t w;
+                        asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0xFFC0u) << 1)));
+                        const uint32_t chunk = (uint32_t)(4 * cb + 2 * ks + c);
+                        const uint32_t dst = ast + (uint32_t)(2 * ms + d) * 1024u + ((chunk ^ (uint32_t)a) << 4);
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(w) : "memory");
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int tt = 0; tt < 4; tt++) {
+                    const int ks = tt >> 1, ms = tt & 1;
+                    uint32_t wv[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {          // eight states, K bits apart, two weights per word
+                        const uint32_t s0 = (uint32_t)(pbits[tt] >> (32 - 2 * j * K)) & 0xFFFFu;
+                        const uint32_t s1 = (uint32_t)(pbits[tt] >> (32 - (2 * j + 1) * K)) & 0xFFFFu;
+                        const __half lo = CODE == QTIP_CODE_3INST ? decode_3inst(s0) : decode_1mad_tab(s0, mad_tab);
+                        const __half hi = CODE == QTIP_CODE_3INST ? decode_3inst(s1) : decode_1mad_tab(s1, mad_tab);
+                        const __half2 p2 = __halves2half2(lo, hi);
+                        wv[j] = *reinterpret_cast<const uint32_t *>(&p2);
+                    }
+                    // row 32rb + 16ms + pr of the stage, 16-byte chunk 4cb + 2ks + ph of its 128-byte row
+                    const uint32_t row = (uint32_t)(32 * rb + 16 * ms + pr), chunk = (uint32_t)(4 * cb + 2 * ks + ph);
+                    const uint32_t dst = a_base + s * kAStageBytes + (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
@@ -230,7 +297,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
         for (int step = 0; step < nsteps; step++) {
             const int s = step % kStages, round = step / kStages;
-            mbar_wait(smem_addr(&ctl->full[s]), round & 1, abort_flag, status, 2u);
+            // a wait that gave up ends the issue loop: no further MMA is started, and the commit below still
+            // covers everything issued so far
+            if (!mbar_wait(smem_addr(&ctl->full[s]), round & 1, abort_flag, status, 2u)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t adesc = umma_desc(a_base + s * kAStageBytes);
             const uint64_t bdesc = umma_desc(b_base + s * b_stage_bytes);
@@ -269,25 +338,44 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == kDecodeWarps) {
+        // tensor memory is released only after the last commit has arrived, i.e. after every MMA that was issued has
+        // completed - also on the abort path, where the epilogue warps did not wait for it
+        if (lane == 0) mbar_wait_bounded(smem_addr(&ctl->done), 0u);
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
     }
 }
 
-template <int K>
+template <int K, int CODE>
 int launch_gemm(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs, int npad,
                 int splitk, unsigned *status, cudaStream_t s) {
     const int smem = 1024 + kStages * (kAStageBytes + npad * 128) + kLut512Bytes + 256;
     static bool attr_set[64] = {};
+    static std::mutex attr_mutex;
     int dev = 0;
     QTIP_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-        QTIP_CUDA_TRY(cudaFuncSetAttribute(decompress_gemm_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr_set[dev] = true;
+    if (dev < 0 || dev >= 64) return QTIP_ERR_BAD_ARG;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        if (!attr_set[dev]) {
+            QTIP_CUDA_TRY(cudaFuncSetAttribute(decompress_gemm_kernel<K, CODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               227 * 1024));
+            attr_set[dev] = true;
+        }
     }
     if (splitk > 1) QTIP_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)bs * m * sizeof(float), s));
-    decompress_gemm_kernel<K><<<dim3(m / kRows, splitk), kGemmThreads, smem, s>>>(out, codes, x, tlut, m, n, bs, npad, splitk,
-                                                                                  status);
+    decompress_gemm_kernel<K, CODE><<<dim3(m / kRows, splitk), kGemmThreads, smem, s>>>(out, codes, x, tlut, m, n, bs, npad,
+                                                                                        splitk, status);
     return check_launch();
+}
+
+template <int CODE>
+int launch_gemm_k(float *out, const uint8_t *c, const __half *xh, const uint32_t *t, int K, int m, int n, int bs, int npad,
+                  int splitk, unsigned *status, cudaStream_t s) {
+    if (K == 2) return launch_gemm<2, CODE>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+    if (K == 3) return launch_gemm<3, CODE>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+    return launch_gemm<4, CODE>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
 }
 
 }  // namespace
@@ -309,7 +397,21 @@ extern "C" int qtip_decompress_gemm(float *out, const void *codes, const void *x
     auto *xh = static_cast<const __half *>(x);
     auto *t = static_cast<const uint32_t *>(tlut);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (K == 2) return launch_gemm<2>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
-    if (K == 3) return launch_gemm<3>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
-    return launch_gemm<4>(out, c, xh, t, m, n, bs, npad, splitk, status, s);
+    return launch_gemm_k<QTIP_CODE_HYB>(out, c, xh, t, K, m, n, bs, npad, splitk, status, s);
+}
+
+extern "C" int qtip_decompress_gemm_plain(float *out, const void *codes, const void *x, int code, int K, int m, int n, int bs,
+                                          unsigned *status, void *stream) {
+    if (!out || !codes || !x || !status || K < 2 || K > 4 || bs < 1 || bs > kMaxN) return QTIP_ERR_BAD_ARG;
+    if (code != QTIP_CODE_3INST && code != QTIP_CODE_1MAD) return QTIP_ERR_BAD_ARG;
+    if (m <= 0 || n <= 0 || (m % kRows) || (n % kStageCols)) return QTIP_ERR_BAD_SHAPE;
+    if ((long)(m >> 5) * (n >> 5) >= (1L << 30)) return QTIP_ERR_BAD_SHAPE;
+    if (!aligned(codes, 16) || !aligned(x, 16) || !aligned(out, 4) || !aligned(status, 4)) return QTIP_ERR_ALIGNMENT;
+    const int npad = (bs + 15) & ~15;
+    const int splitk = ((m / kRows) * 2 <= sm_count() && (n % (2 * kStageCols)) == 0) ? 2 : 1;
+    auto *c = static_cast<const uint8_t *>(codes);
+    auto *xh = static_cast<const __half *>(x);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (code == QTIP_CODE_3INST) return launch_gemm_k<QTIP_CODE_3INST>(out, c, xh, nullptr, K, m, n, bs, npad, splitk, status, s);
+    return launch_gemm_k<QTIP_CODE_1MAD>(out, c, xh, nullptr, K, m, n, bs, npad, splitk, status, s);
 }

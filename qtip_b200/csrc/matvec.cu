@@ -531,7 +531,7 @@ __device__ __forceinline__ void fused_output_regs(const FusedOut &O, const float
 template <int K, bool XS, bool TP, int NW, int C>
 __global__ void __launch_bounds__(NW * 32, 1)
     matvec_hyb_kernel(const __grid_constant__ MatvecBatch batch, int m, int n, int bs, int kmax, int mode, int db,
-                      int xs_offset) {
+                      int xs_offset, int scratch_offset) {
     constexpr int kBlockBytes = 128 * K;
     constexpr int chunk_blocks = C;
     const bool DB = db != 0;
@@ -541,8 +541,8 @@ __global__ void __launch_bounds__(NW * 32, 1)
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: control block (incl. two mbarriers per warp) | LUT | ring slot 0 [NW][chunk] | ring slot 1 [NW][chunk] |
     //         reduction buffer(s) [NW][bs][32] fp32 | (padding) | x (bs, n) fp16 permuted
-    // The fp32 scratch of the fused input transform overlays ring slot 1 and what follows it up to x: slot 1 is
-    // first filled after the transform is done.
+    // The fp32 scratch of the fused input transform lies behind x when everything fits (scratch_offset > 0); otherwise
+    // it overlays ring slot 1 and what follows it up to x, and slot 1 is first filled after the transform is done.
     const MatvecProblem &P = batch.p[blockIdx.y];
     float *__restrict__ out = P.out;
     const uint8_t *__restrict__ codes = P.codes;
@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(NW * 32, 1)
     float *red = reinterpret_cast<float *>(ring + 2 * NW * slot_bytes);
     (void)chunk_blocks;
     uint4 *xs = reinterpret_cast<uint4 *>(smem + xs_offset);
-    float *fscratch = reinterpret_cast<float *>(ring + NW * slot_bytes);
+    float *fscratch = reinterpret_cast<float *>(scratch_offset > 0 ? smem + scratch_offset : ring + NW * slot_bytes);
 
     unsigned *counters = reinterpret_cast<unsigned *>(P.workspace);
     unsigned *done_counter = reinterpret_cast<unsigned *>(P.workspace + kCounterBytes);
@@ -617,6 +617,7 @@ __global__ void __launch_bounds__(NW * 32, 1)
     // First chunk of this warp: packed codes are weights, so the copy starts before the table build and before
     // waiting for the previous kernel of the stream.
     issue();
+    if (scratch_offset > 0) issue();      // ring slot 1 is free from the start: second chunk in flight as well
     if (threadIdx.x == 0) sh->is_last = 0;
     // lane-private LUT copies: entry e = sign << 9 | index, copy l at byte e*128 + l*4; the sign bit
     // flips the sign of the first (low) half of the pair.  Thread t writes the 16-byte groups t, t + kThreads, ...:
@@ -773,7 +774,7 @@ __global__ void __launch_bounds__(NW * 32, 1)
         }
     }
     __syncthreads();
-    issue();   // second chunk: ring slot 1 (the scratch of the fused input side lay over it until the barrier above)
+    if (scratch_offset <= 0) issue();   // second chunk: ring slot 1 (the scratch of the fused input side lay over it until now)
 
     const int g = lane >> 2, t = lane & 3;
     const int xg = g < bs ? g : 0;  // lanes of unused batch columns alias row 0; their results are never stored
@@ -903,10 +904,10 @@ __global__ void __launch_bounds__(NW * 32, 1)
 // column 4t+e, fragment column 2t+8+e is matrix column 4t+2+e) and x is loaded with the same
 // permutation, which leaves every dot product unchanged.
 template <int CODE>
-__device__ __forceinline__ uint32_t decode_pair(uint32_t s0, uint32_t s1) {
+__device__ __forceinline__ uint32_t decode_pair(uint32_t s0, uint32_t s1, const __half *mad_tab) {
     __half lo, hi;
     if constexpr (CODE == QTIP_CODE_3INST) { lo = decode_3inst(s0 & 0xFFFFu); hi = decode_3inst(s1 & 0xFFFFu); }
-    else { lo = decode_1mad(s0 & 0xFFFFu); hi = decode_1mad(s1 & 0xFFFFu); }
+    else { lo = decode_1mad_tab(s0 & 0xFFFFu, mad_tab); hi = decode_1mad_tab(s1 & 0xFFFFu, mad_tab); }
     __half2 p = __halves2half2(lo, hi);
     return *reinterpret_cast<uint32_t *>(&p);
 }
@@ -933,6 +934,11 @@ __global__ void __launch_bounds__(kPlainWarps * 32, 2)
     extern __shared__ __align__(128) uint8_t smem[];
     Shared *sh = reinterpret_cast<Shared *>(smem);
     float *red = reinterpret_cast<float *>(smem + kCtrlBytes);
+    __shared__ __half mad_tab[CODE == QTIP_CODE_1MAD ? kMadTableEntries : 1];
+    if constexpr (CODE == QTIP_CODE_1MAD) {
+        build_1mad_table(mad_tab);
+        __syncthreads();
+    }
     unsigned *counters = reinterpret_cast<unsigned *>(workspace);
     float *partial = reinterpret_cast<float *>(workspace + kPartialOffset);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -965,8 +971,8 @@ __global__ void __launch_bounds__(kPlainWarps * 32, 2)
                     const uint64_t bits = tile_bits48(words, nwords, e0 * K);
                     const uint32_t s0 = (uint32_t)(bits >> 32), s1 = (uint32_t)(bits >> (32 - K));
                     const uint32_t s2 = (uint32_t)(bits >> (32 - 2 * K)), s3 = (uint32_t)(bits >> (32 - 3 * K));
-                    a[hr] = decode_pair<CODE>(s0, s1);       // a0 / a1: fragment cols 2t, 2t+1
-                    a[2 + hr] = decode_pair<CODE>(s2, s3);   // a2 / a3: fragment cols 2t+8, 2t+9
+                    a[hr] = decode_pair<CODE>(s0, s1, mad_tab);       // a0 / a1: fragment cols 2t, 2t+1
+                    a[2 + hr] = decode_pair<CODE>(s2, s3, mad_tab);   // a2 / a3: fragment cols 2t+8, 2t+9
                 }
                 mma_16816(acc[ms], a, b0, b1);
             }
@@ -987,7 +993,7 @@ int check_common(const void *out, const void *codes, const void *x, int K, int m
 }
 
 struct SmemPlan {
-    int chunk_blocks, xs_offset, total, db;
+    int chunk_blocks, xs_offset, total, db, scratch_offset;
 };
 
 template <int K, bool XS, bool TP, int NW, int C>
@@ -1017,7 +1023,7 @@ int launch_hyb_variant_tp(const MatvecBatch &batch, int nprob, int m, int n, int
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     QTIP_CUDA_TRY(cudaLaunchKernelEx(&cfg, matvec_hyb_kernel<K, XS, TP, NW, C>, batch, m, n, bs, p.kmax, p.mode, plan.db,
-                                     plan.xs_offset));
+                                     plan.xs_offset, plan.scratch_offset));
     return check_launch();
 }
 
@@ -1053,8 +1059,17 @@ bool plan_smem(int n, int bs, bool xs, bool db, bool fused_in, SmemPlan &plan) {
     const int scratch_bytes = fused_in ? (n + (n >> 5) + 136) * (int)sizeof(float) : 0;
     const int avail = kSmemLimit - kCtrlBytes - kLutBytes;
     plan.db = db ? 1 : 0;
+    plan.scratch_offset = 0;
     for (int c = kMaxChunkBytes / BB; c >= 1; c >>= 1) {          // 4, 2, 1: the instantiated chunk sizes
         const int slot = NW * c * BB;                                   // one ring slot, all warps
+        if (2 * slot + red_bytes + x_bytes + scratch_bytes <= avail) {  // room for a scratch area of its own
+            plan.chunk_blocks = c;
+            plan.xs_offset = kCtrlBytes + kLutBytes + 2 * slot + red_bytes;
+            plan.scratch_offset = scratch_bytes > 0 ? plan.xs_offset + x_bytes : 1;   // > 0: both ring slots usable at once
+            plan.total = kCtrlBytes + kLutBytes + 2 * slot + red_bytes + x_bytes + scratch_bytes;
+            if (plan.scratch_offset == 1) plan.scratch_offset = plan.xs_offset;       // no scratch needed: any offset > 0
+            return true;
+        }
         const int after_slot1 = slot + red_bytes;                       // bytes from slot 1 up to x
         const int pad = scratch_bytes > after_slot1 ? scratch_bytes - after_slot1 : 0;
         const int total = 2 * slot + red_bytes + pad + x_bytes;

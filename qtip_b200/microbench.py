@@ -19,6 +19,7 @@ import torch
 from . import _lib, ops, synth
 
 LLAMA7B = "4096x4096,11008x4096,4096x11008"
+_PLAIN_MATVEC = False   # --plain-matvec: time qtip_decompress_matvec_plain instead of the tensor-core kernel (batch <= 8)
 
 
 def _sets(m, n, K, bs, code, device, min_bytes=400e6, max_sets=48):
@@ -32,6 +33,8 @@ def _launch(lay, code, K, m, n, out, ws):
         ops.decompress_gemm(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out)      # tcgen05 path, batches 9..64
     elif code == "hyb":
         ops.decompress_matvec(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out, workspace=ws)
+    elif ops.gemm_plain_supported(m, n, lay["x"].shape[0]) and not _PLAIN_MATVEC:
+        ops.decompress_gemm_plain(lay["codes"], lay["x"], code, K, m, n, out=out)      # compute codes on the tcgen05 path
     else:
         ops.decompress_matvec_plain(lay["codes"], lay["x"], code, K, m, n, out=out, workspace=ws)
 
@@ -129,7 +132,11 @@ def main():
     ap.add_argument("--code", default="hyb", choices=["hyb", "3inst", "1mad"])
     ap.add_argument("--plain-launches", type=int, default=0)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--plain-matvec", action="store_true",
+                    help="compute codes, batch <= 8: time the mma.sync matvec instead of the tcgen05 kernel")
     args = ap.parse_args()
+    global _PLAIN_MATVEC
+    _PLAIN_MATVEC = args.plain_matvec
     peak = None
     try:
         import os

@@ -463,5 +463,31 @@ def decompress_gemm(codes, x, tlut, K, m, n, out=None):
     return out
 
 
+def decompress_gemm_plain(codes, x, code, K, m, n, out=None):
+    """decompress_gemm for the 3INST / 1MAD compute codes (plain layout, V = 1), 1 <= bs <= 64."""
+    _require_cuda(codes, x)
+    code = CODE_IDS.get(code, code)
+    if x.dtype != torch.float16:
+        x = x.to(torch.float16)
+    x = x.reshape(-1, n).contiguous()
+    bs = x.shape[0]
+    if out is None:
+        out = torch.empty(bs, m, dtype=torch.float32, device=x.device)
+    key = x.device.index
+    if key not in _gemm_status:
+        _gemm_status[key] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().qtip_decompress_gemm_plain(out.data_ptr(), codes.data_ptr(), x.data_ptr(), code, K, m, n, bs,
+                                                    _gemm_status[key].data_ptr(), _stream())
+    _lib.check(st, "qtip_decompress_gemm_plain")
+    global launch_count
+    launch_count += 1
+    return out
+
+
+def gemm_plain_supported(m, n, bs):
+    return 1 <= bs <= MAX_GEMM_BATCH and m % 128 == 0 and n % 64 == 0
+
+
 def gemm_supported(m, n, bs):
     return MAX_MATVEC_BATCH < bs <= MAX_GEMM_BATCH and m % 128 == 0 and n % 64 == 0

@@ -199,6 +199,22 @@ def test_decompress_gemm(K, m, n, bs):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("code", [O.CODE_3INST, O.CODE_1MAD])
+@pytest.mark.parametrize("K,m,n,bs", [(2, 128, 64, 16), (2, 1024, 2048, 32), (3, 256, 256, 9), (4, 512, 1024, 64),
+                                      (2, 8192, 8192, 16)])
+def test_decompress_gemm_plain_vs_oracle(code, K, m, n, bs):
+    """Compute codes (V = 1, plain layout) on the tensor-core path against the CPU oracle: bit-exact decode
+    (C.decode_plain with the oracle's state table) + dense product with fp32 accumulation."""
+    lay = synth.make_layer(m, n, K, seed=3500 + K, bs=bs, code="none")
+    y = ops.decompress_gemm_plain(dev(lay["codes"]), dev(lay["x"]), code, K, m, n)
+    torch.cuda.synchronize()
+    want = C.matvec_dense(C.decode_plain(lay["codes"], m, n, K, 1, O.state_table(code)), lay["x"])
+    assert ops.gemm_status(DEV) == 0, "a bounded barrier wait inside the kernel gave up"
+    assert rel_l2(y.cpu().numpy(), want) < 1e-5
+    assert torch.equal(y, ops.decompress_gemm_plain(dev(lay["codes"]), dev(lay["x"]), code, K, m, n))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("K,m,n,bs", [(2, 1024, 2048, 16), (4, 256, 256, 40)])
 def test_decompress_gemm_vs_oracle(K, m, n, bs):
     """The tensor-core path directly against the CPU oracle (decode of the kernel layout + dense product), with no
