@@ -279,6 +279,65 @@ def measure_decoder_gbs(torch, K=2, m=4096, n=11008):
     return (K * m * n / 8 + 2 * m * n) / us / 1e3, us
 
 
+def run_gpu_batch(args, model, torch, dist, world, rank, dev):
+    """--batch B: B sequences decoded in lockstep (QtipLlama.step_batch, one CUDA graph per step).  The KV caches are
+    brought to the prompt length by decoding (every sequence samples its own tokens)."""
+    B, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
+    model.enable_batch(B)
+    model.b_token.copy_(torch.arange(B, device=dev) * 7 + 3)
+    model.capture_batch()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with ClockSampler(int(dev.split(":")[1])) as clocks:
+        model.steps_done = 0
+        model.generate_batch(args.prompt + warmup)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        model.generate_batch(steps)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        h_tok = torch.zeros(B, dtype=torch.int64).pin_memory()
+        h_out = torch.zeros(B, dtype=torch.int64).pin_memory()
+        h_tok.copy_(model.b_token.cpu())
+        barrier()
+        model._reserve(steps)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            model.b_token.copy_(h_tok, non_blocking=True)
+            model.b_graph.replay()
+            h_out.copy_(model.b_token, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            h_tok.copy_(h_out)
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+    model.check_status()
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank == 0:
+        cfg = workload_config(args.workload, args.prompt, world)
+        cfg["workload"] = cfg["workload"].replace("batch 1", f"batch {B} (sequences in lockstep)")
+        out = {"metric": metric_name(args.workload).replace("bs=1", f"bs={B}"), "value": B * steps / (ms / 1e3), "unit": "tok/s",
+               "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+               "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+               "config": cfg, "roofline": None, "cpu_baseline": None,
+               "e2e": {"value": B * steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+               "gpu_launches": model.n_launches_per_batch_step * steps, "clocks": clocks.summary()}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        model.release_graph()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -297,8 +356,10 @@ def run_gpu(args):
     torch.cuda.manual_seed(1234)  # (the sampler itself is keyed by the model seed and the position: same draws on every rank)
     # N > 1: the one sequence is decoded tensor-parallel over the N GPUs (column/row-parallel shards, per-GPU
     # Hadamard transforms; the partial results of o_proj / down_proj are summed through peer-mapped memory)
-    model = QtipLlama(shape, max_positions=args.prompt + 2 * (warmup + steps) + 8, device=dev, seed=3000,
+    model = QtipLlama(shape, max_positions=args.prompt + 2 * (warmup + steps) + 16, device=dev, seed=3000,
                       tp_rank=rank, tp_size=world, group=dist.group.WORLD if world > 1 else None, fuse_qkv=args.fuse_qkv)
+    if args.batch > 1:
+        return run_gpu_batch(args, model, torch, dist, world, rank, dev)
     model.capture()
     g = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, shape.vocab, (args.prompt,), generator=g)
@@ -411,6 +472,8 @@ def main():
     ap.add_argument("--workload", default="llama2-7b", choices=["llama2-7b", "llama3-405b"],
                     help="llama3-405b: the 126-layer shape of the tensor-parallel configuration (256-token prompt)")
     ap.add_argument("--impl", default="qtip_b200", choices=["qtip_b200", "reference"])
+    ap.add_argument("--batch", type=int, default=1,
+                    help="sequences decoded in lockstep (<= 8; the batch rides in the matvec launches); value counts all of them")
     ap.add_argument("--fuse-qkv", action="store_true",
                     help="q||k||v and gate||up as ONE matrix each (12288x4096, 22016x4096 at the 7B shape), the layout "
                          "upstream's published 188 tok/s was measured with")

@@ -399,6 +399,106 @@ class QtipLlama:
         ops.sample_top_k(self.token, self.out_tokens, self.pos, self.logits, temperature=0.6, top_k=5, seed=self.sample_seed,
                          status=self.status)
 
+    # -- batched decode: B sequences in lockstep ------------------------------------------------------
+    def enable_batch(self, B):
+        """Buffers for decoding B (<= 8) independent sequences per step (step_batch).  The batch rides in the matvec
+        launches (the packed matrices are streamed once for all B rows); the transforms run as row-batched launches of
+        the transform kernel, rotary embedding / attention / sampling per sequence.  Works for every shape and for
+        tensor parallelism (NCCL all-reduce after o_proj and down_proj)."""
+        assert 1 <= B <= ops.MAX_MATVEC_BATCH and not self.fuse_qkv
+        s, dev, H, KV, MLP = self.shape, self.device, self.H, self.KV, self.MLP
+        f16 = dict(dtype=torch.float16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.B = B
+        self.b_token = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.b_pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.b_res = [torch.zeros(B, s.hidden, **f16), torch.zeros(B, s.hidden, **f16)]
+        self.b_delta = torch.zeros(B, s.hidden, **f16)
+        self.b_xh = torch.zeros(B, max(s.hidden, MLP, H), **f16)
+        self.b_y = torch.zeros(B, max(s.hidden, MLP, H), **f32)
+        self.b_q, self.b_k, self.b_v = torch.zeros(B, H, **f16), torch.zeros(B, KV, **f16), torch.zeros(B, KV, **f16)
+        self.b_attn = torch.zeros(B, H, **f16)
+        self.b_g, self.b_u = torch.zeros(B, MLP, **f16), torch.zeros(B, MLP, **f16)
+        self.b_cache_k = torch.zeros(B, s.n_layers, self.max_positions, KV, **f16)
+        self.b_cache_v = torch.zeros_like(self.b_cache_k)
+        self.b_logits = torch.zeros(B, s.vocab, **f32)
+        self.b_out_tokens = torch.zeros(B, self.max_positions + 1, dtype=torch.int64, device=dev)
+        need = max(ops._lib.load().qtip_matvec_workspace_bytes(m, n, B)
+                   for (m, n) in ((H, s.hidden), (MLP, s.hidden), (s.hidden, MLP), (s.hidden, H), (KV, s.hidden)))
+        self.b_workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        self.b_graph = None
+
+    def _b_linear(self, lin, src, *, residual=None, residual_out=None, norm=None, gate=None, kf_in, kf_out,
+                  out, all_reduce=False):
+        """One QTIP linear on B rows: transform in (optionally residual add / RMSNorm / SwiGLU), matvec, transform out."""
+        B, n, m = self.B, lin.n, lin.m
+        xh, y = self.b_xh.view(-1)[:B * n].view(B, n), self.b_y.view(-1)[:B * m].view(B, m)
+        ops.rht_fused(src, B, n, xh, residual=residual, residual_out=residual_out, norm_weight=norm, eps=self.shape.rms_eps,
+                      gate=gate, sign_in=lin.SU, hadk_bits=self.bits[kf_in], kfac=kf_in, transpose=True,
+                      scale=1 / math.sqrt(n) / 32)
+        ops.decompress_matvec(lin.codes, xh, lin.tlut, lin.K, m, n, out=y, workspace=self.b_workspace)
+        if all_reduce:
+            self._all_reduce(y)
+        ops.rht_fused(y, B, m, out, sign_out=lin.SV32, hadk_bits=self.bits[kf_out], kfac=kf_out, scale=1 / math.sqrt(m))
+
+    def step_batch(self):
+        """One decode step of B sequences on the static batch buffers: b_token -> next tokens, b_pos += 1."""
+        s, B = self.shape, self.B
+        ra, rb = self.b_res
+        torch.index_select(self.embed, 0, self.b_token, out=ra)
+        self.b_delta.zero_()
+        for li, L in enumerate(self.layers):
+            # res_b = res_a + delta ; h = RMSNorm(res_b) ; q, k, v
+            self._b_linear(L["q"], self.b_delta, residual=ra, residual_out=rb, norm=L["ln1"], kf_in=self.kf_h,
+                           kf_out=self.kf_hl, out=self.b_q)
+            self._b_linear(L["k"], rb, norm=L["ln1"], kf_in=self.kf_h, kf_out=self.kf_kv, out=self.b_k)
+            self._b_linear(L["v"], rb, norm=L["ln1"], kf_in=self.kf_h, kf_out=self.kf_kv, out=self.b_v)
+            for b in range(B):
+                ck, cv, pos = self.b_cache_k[b, li], self.b_cache_v[b, li], self.b_pos[b:b + 1]
+                ops.rope_kv_append(self.b_q[b], self.b_k[b], self.b_v[b], ck, cv, pos, self.n_heads, self.n_kv_heads,
+                                   s.head_dim, s.rope_theta, status=self.status)
+                ops.attn_decode(self.b_attn[b], self.b_q[b], ck, cv, pos, self.n_heads, self.n_kv_heads, s.head_dim,
+                                status=self.status)
+            self._b_linear(L["o"], self.b_attn, kf_in=self.kf_hl, kf_out=self.kf_h, out=self.b_delta, all_reduce=True)
+            # res_a = res_b + delta ; h = RMSNorm(res_a) ; gate, up ; down(silu(gate) * up)
+            self._b_linear(L["gate"], self.b_delta, residual=rb, residual_out=ra, norm=L["ln2"], kf_in=self.kf_h,
+                           kf_out=self.kf_m, out=self.b_g)
+            self._b_linear(L["up"], ra, norm=L["ln2"], kf_in=self.kf_h, kf_out=self.kf_m, out=self.b_u)
+            self._b_linear(L["down"], self.b_u, gate=self.b_g, kf_in=self.kf_m, kf_out=self.kf_h, out=self.b_delta,
+                           all_reduce=True)
+        # final norm + unquantized lm_head for the whole batch (fp16 GEMM: not part of the QTIP path), then the sampler
+        x32 = (ra + self.b_delta).float()
+        hn = (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + s.rms_eps)).half() * self.ln_f
+        self.b_logits.copy_(torch.matmul(hn, self.lm_head.T))
+        for b in range(B):
+            ops.sample_top_k(self.b_token[b:b + 1], self.b_out_tokens[b], self.b_pos[b:b + 1], self.b_logits[b:b + 1],
+                             temperature=0.6, top_k=5, seed=self.sample_seed + b, status=self.status)
+
+    def capture_batch(self):
+        tok, pos = self.b_token.clone(), self.b_pos.clone()
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.step_batch()
+            self.b_token.copy_(tok); self.b_pos.copy_(pos)
+            before = ops.launch_count
+            self.step_batch()
+            self.n_launches_per_batch_step = ops.launch_count - before
+            self.b_token.copy_(tok); self.b_pos.copy_(pos)
+            stream.synchronize()
+            self.b_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.b_graph, stream=stream):
+                self.step_batch()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.b_token.copy_(tok); self.b_pos.copy_(pos)
+        torch.cuda.synchronize(self.device)
+
+    def generate_batch(self, n_tokens):
+        self._reserve(n_tokens)
+        run = self.b_graph.replay if self.b_graph is not None else self.step_batch
+        for _ in range(n_tokens):
+            run()
+
     # -- driving ----------------------------------------------------------------------------------
     def capture(self):
         """Capture step() into a CUDA graph (two eager warm-up steps first; state is restored)."""
@@ -428,6 +528,10 @@ class QtipLlama:
             torch.cuda.synchronize(self.device)
             self.graph.reset()
             self.graph = None
+        if getattr(self, "b_graph", None) is not None:
+            torch.cuda.synchronize(self.device)
+            self.b_graph.reset()
+            self.b_graph = None
 
     def reset(self):
         self.pos.zero_()

@@ -144,3 +144,27 @@ def test_decode_step_at_the_benchmarked_shape_matches_the_oracle(fuse_qkv):
     torch.cuda.synchronize()
     assert torch.equal(model.logits, eager)
     model.check_status()
+
+
+def test_batched_decode_matches_single_sequence_decode():
+    """step_batch (B sequences in lockstep, unfused launches, batch rows inside the matvec) against step() run once per
+    sequence on the same tokens."""
+    shape = LlamaShape(n_layers=2, hidden=4096, n_heads=32, n_kv_heads=32, head_dim=128, mlp=11008, vocab=2048, K=2)
+    seqs = [[5, 900, 33], [1200, 7, 7], [64, 65, 66]]
+    model = QtipLlama(shape, max_positions=8, device=DEV, seed=31)
+    want = []
+    for toks in seqs:
+        model.reset()
+        for t in toks:
+            model.token.fill_(t)
+            model.step()
+        want.append(model.logits.clone().reshape(-1))
+    model.enable_batch(len(seqs))
+    for i in range(3):
+        model.b_token.copy_(torch.tensor([s_[i] for s_ in seqs], device=DEV))
+        model.step_batch()
+    torch.cuda.synchronize()
+    assert model.b_pos.tolist() == [3, 3, 3]
+    for b in range(len(seqs)):
+        assert rel_l2(model.b_logits[b].cpu().numpy(), want[b].cpu().numpy()) < 5e-3
+    model.check_status()
