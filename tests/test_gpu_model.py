@@ -168,3 +168,32 @@ def test_batched_decode_matches_single_sequence_decode():
     for b in range(len(seqs)):
         assert rel_l2(model.b_logits[b].cpu().numpy(), want[b].cpu().numpy()) < 5e-3
     model.check_status()
+
+
+def test_state_dict_round_trip_into_decode_model():
+    """A synthetic checkpoint with upstream's keys, shapes and dtypes (lib/linear/quantized_linear.py:41-67) loaded into
+    a differently seeded model reproduces the source model's logits bit for bit; wrong shapes and tensor-parallel
+    layouts are refused."""
+    from qtip_b200.checkpoint import export_state_dict, load_state_dict_into
+    qp = dict(L=16, K=2, V=2, tlut_bits=9, decode_mode="quantlut_sym", td_x=16, td_y=16, skip_list=None)
+    src = QtipLlama(TINY, max_positions=8, device=DEV, seed=41)
+    sd = export_state_dict(src)
+    assert sd["model.layers.0.self_attn.q_proj.trellis"].dtype == torch.int16
+    assert sd["model.layers.1.mlp.down_proj.SV"].dtype == torch.float32 and sd["model.layers.0.mlp.up_proj.tlut"].shape == (512, 2)
+    dst = load_state_dict_into(QtipLlama(TINY, max_positions=8, device=DEV, seed=42), sd, qp)
+    out = []
+    for model in (src, dst):
+        model.reset()
+        for t in (3, 9, 27):
+            model.token.fill_(t)
+            model.step()
+        out.append(model.logits.clone())
+    assert torch.equal(out[0], out[1])
+    bad = dict(sd)
+    bad["model.layers.0.mlp.up_proj.trellis"] = bad["model.layers.0.mlp.up_proj.trellis"][:-1]
+    with pytest.raises(ValueError, match="up_proj.trellis"):
+        load_state_dict_into(QtipLlama(TINY, max_positions=8, device=DEV, seed=43), bad, qp)
+    bad = dict(sd)
+    bad["model.layers.1.self_attn.o_proj.rcp"] = torch.tensor(1)
+    with pytest.raises(ValueError, match="rcp"):
+        load_state_dict_into(QtipLlama(TINY, max_positions=8, device=DEV, seed=43), bad, qp)

@@ -117,3 +117,23 @@ def test_decode_model_refuses_more_positions_than_the_cache_holds():
     with pytest.raises(RuntimeError, match="KV cache holds 10"):
         m._reserve(1)
     assert m.steps_done == 10
+
+
+def test_quip_params_validation():
+    """The config dict upstream stores in the HF config: what the decode path builds is accepted, everything else is
+    refused with the key named (quantize_llama/quantize_finetune_llama.py:116-129, model/llama.py:306-317, 445-452)."""
+    from qtip_b200.checkpoint import check_quip_params
+    from qtip_b200.llama import LlamaShape
+    shape = LlamaShape(K=2)
+    ok = dict(codebook="bitshift", codebook_version=0, L=16, K=2, V=2, tlut_bits=9, decode_mode="quantlut_sym", td_x=16,
+              td_y=16, split_for_tp=False, skip_list=None)
+    assert check_quip_params(ok, shape) == 2
+    for key, bad in (("L", 12), ("V", 1), ("tlut_bits", 8), ("decode_mode", "3inst"), ("td_x", 8), ("K", 5)):
+        with pytest.raises(ValueError, match=key):
+            check_quip_params(dict(ok, **{key: bad}), shape)
+    with pytest.raises(ValueError, match="K_v_proj"):
+        check_quip_params(dict(ok, K_v_proj=3), shape)
+    with pytest.raises(ValueError, match="skip_list"):
+        check_quip_params(dict(ok, skip_list=["0_q"]), shape)
+    with pytest.raises(ValueError, match="built for K"):
+        check_quip_params(dict(ok, K=3), shape)
