@@ -30,7 +30,8 @@ PROMPT_TOKENS = 128
 PUBLISHED_TOK_S = 188.0  # upstream README.md:31-38, Llama-2-7B 2-bit on an RTX 6000 Ada (fused q/k/v and up/gate)
 # DRAM bytes (read + write) of one decode-matvec launch per layer shape, from an ncu capture of the same kernel
 # instantiation on plain launches over rotating weights (dram__bytes_read.sum + dram__bytes_write.sum)
-NCU_TRAFFIC_BYTES = {(4096, 4096): 4283136, (11008, 4096): 11361280, (4096, 11008): 11375872}
+NCU_TRAFFIC_BYTES = {(4096, 4096): 4536405, (11008, 4096): 11697152, (4096, 11008): 11798443, (12288, 4096): 13007189,
+                     (22016, 4096): 22975915}
 WORKLOADS = {
     "llama2-7b": dict(name="Llama-2-7B", n_layers=32, hidden=4096, n_heads=32, n_kv_heads=32, head_dim=128, mlp=11008,
                       vocab=32000, rope_theta=10000.0),
@@ -422,9 +423,10 @@ def run_gpu(args):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = byts / us / 1e3  # GB/s
-        traffic = [NCU_TRAFFIC_BYTES.get(s) for s in llama7b_linears()]
         seven_b = args.workload == "llama2-7b"
-        traffic = None if world > 1 or not seven_b or args.fuse_qkv or any(t is None for t in traffic) else sum(traffic) / len(traffic)
+        shapes = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)] if args.fuse_qkv else llama7b_linears()
+        traffic = [NCU_TRAFFIC_BYTES.get(s) for s in shapes]
+        traffic = None if world > 1 or not seven_b or any(t is None for t in traffic) else sum(traffic) / len(traffic)
         extra = {}
         if world == 1 and seven_b:
             layer_us, h2d, d2h = measure_layer_e2e(torch)

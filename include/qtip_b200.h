@@ -60,6 +60,23 @@ int qtip_decode_hyb(void *W, const void *codes, const void *tlut, int K, int m, 
 int qtip_decode_plain(void *W, const void *codes, int code, const void *tlut, int K, int m, int n, void *stream);
 
 /* --------------------------------------------------------------------------------------------
+ * Producers of the packed formats (the quantizer side of the format; pure bit / byte movement, bit-exact).
+ * ------------------------------------------------------------------------------------------ */
+
+/* bitshift_codebook.pack_trellis (lib/codebook/bitshift.py:294-327): trellis states -> packed words, plain layout.
+ * states: (tiles, 256/V) int32, each a 16-bit state (L = 16); words: (tiles, 16*K) uint16 - the tile's tail-biting
+ * bitstream, MSB first: state 0's 16 bits, then the low K*V bits of each later state, the last 16 - K*V bits dropped.
+ * violations (optional, one zero-initialised uint32): receives the number of consecutive state pairs that do not
+ * overlap by 16 - K*V bits (upstream asserts this, :306-309); the words are written either way. */
+int qtip_pack_trellis(void *words, const int *states, long tiles, int K, int V, unsigned *violations, void *stream);
+
+/* The byte shuffle from the plain layout to the kernel layout for L = 16, V = 2, 16x16 tiles
+ * (lib/algo/finetune.py:196-201) and its inverse (lib/utils/kernel_decompress.py:19-24).  Both buffers hold
+ * K*m*n/8 bytes and must not alias; m, n multiples of 32. */
+int qtip_plain_to_kernel_layout(void *kernel_codes, const void *plain_words, int K, int m, int n, void *stream);
+int qtip_kernel_to_plain_layout(void *plain_words, const void *kernel_codes, int K, int m, int n, void *stream);
+
+/* --------------------------------------------------------------------------------------------
  * Fused decode + matvec:  out[b][r] = sum_c W[r][c] * x[b][c],  fp16 operands, fp32 accumulate.
  * ------------------------------------------------------------------------------------------ */
 
@@ -152,6 +169,11 @@ typedef struct qtip_linear_desc {
     unsigned *signal_seq;         /* this GPU's sequence counter, advanced by one per launch */
 } qtip_linear_desc;
 int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream);
+
+/* Writes sizeof(qtip_linear_desc) and then the byte offset of every field, in declaration order, into out (up to
+ * `capacity` entries; out may be NULL) and returns the number of entries (1 + number of fields).  For bindings that
+ * mirror the struct by hand: compare at start-up, refuse to run on a mismatch.  No device is touched. */
+int qtip_linear_desc_layout(size_t *out, int capacity);
 
 /* qtip_decompress_matvec for callers that must not allocate device memory and have none to spare for a
  * workspace - a serving loop that froze its memory pool at start-up, a plug-in whose host owns every

@@ -85,6 +85,25 @@ def main():
             got = O.decode_plain_layout(codes.numpy(), m, n, K, V, code, tlut.numpy())
             check(f"plain decode {mode} K={K}", np.array_equal(want.half().numpy().view(np.uint16), got.view(np.uint16)))
 
+    # --- pack_trellis: upstream on upstream-unpacked states, and on a walk that does not bite its tail ------
+    for K in (2, 3, 4):
+        for mode, V in (("3inst", 1), ("quantlut_sym", 2)):
+            kw = dict(tlut_bits=9, tlut=tlut) if V == 2 else dict(tlut_bits=0)
+            cb = bs_mod.bitshift_codebook(L=16, K=K, V=V, decode_mode=mode, **kw)
+            codes = torch.randint(0, 65536, (24, 16 * K), generator=g).to(torch.uint16)
+            stt = cb.unpack_trellis(codes.view(torch.int16), 256)
+            want = cb.pack_trellis(stt)
+            check(f"pack_trellis round trip (upstream) {mode} K={K}", torch.equal(want.view(torch.int16), codes.view(torch.int16)))
+            check(f"pack_trellis {mode} K={K}", np.array_equal(want.numpy(), O.pack_trellis(stt.numpy(), K, V)))
+            # an open walk (last states do not wrap onto the first): the dropped bits are simply lost
+            T, kv = 256 // V, K * V
+            walk = torch.zeros(5, T, dtype=torch.int64)
+            walk[:, 0] = torch.randint(0, 65536, (5,), generator=g)
+            for i in range(1, T):
+                walk[:, i] = ((walk[:, i - 1] << kv) & 0xFFFF) | torch.randint(0, 1 << kv, (5,), generator=g)
+            check(f"pack_trellis open walk {mode} K={K}",
+                  np.array_equal(cb.pack_trellis(walk).numpy(), O.pack_trellis(walk.numpy(), K, V)))
+
     # --- Hadamard ---------------------------------------------------------------------------------
     for n in (128, 4096, 11008, 6656, 14336):
         x = torch.randn(2, n, generator=g)

@@ -138,6 +138,27 @@ def states_plain_layout(codes, m, n, K, V):
     return st.astype(np.uint16)
 
 
+def pack_trellis(states, K, V):
+    """Trellis states [tiles][256/V] -> plain-layout words [tiles][16*K] uint16.
+
+    pack_trellis (lib/codebook/bitshift.py:294-327): the bitstream of a tile is state 0's 16 bits (MSB first)
+    followed by the low K*V bits of every later state; the last 16 - K*V bits are dropped (a tail-biting walk
+    repeats the first bits there) and the stream is cut into 16-bit words, MSB first.  Raises ValueError where
+    upstream asserts (:306-309): consecutive states must overlap by 16 - K*V bits."""
+    st = np.asarray(states).astype(np.int64)
+    tiles, T = st.shape
+    kv = K * V
+    assert T * V == 256 and (T * kv) % 16 == 0
+    if not np.array_equal(st[:, :-1] & ((1 << (L_BITS - kv)) - 1), st[:, 1:] >> kv):
+        raise ValueError("consecutive states do not overlap")
+    bits = np.zeros((tiles, T * kv + L_BITS - kv), dtype=np.uint8)
+    bits[:, :L_BITS] = (st[:, :1] >> np.arange(L_BITS - 1, -1, -1)) & 1
+    low = (st[:, 1:, None] >> np.arange(kv - 1, -1, -1)) & 1              # tiles, T-1, kv
+    bits[:, L_BITS:] = low.reshape(tiles, -1)
+    bits = bits[:, :T * kv].reshape(tiles, -1, 16).astype(np.uint32)
+    return (bits << np.arange(15, -1, -1, dtype=np.uint32)).sum(axis=2).astype(np.uint16)
+
+
 def decode_plain_layout(codes, m, n, K, V, code, tlut=None):
     """Plain-layout decode -> (m, n) fp16.
 

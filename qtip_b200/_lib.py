@@ -32,12 +32,16 @@ SIGNATURES = {
     "qtip_version": (_i, []),
     "qtip_decode_hyb": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "qtip_decode_plain": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "qtip_pack_trellis": (_i, [_vp, _vp, _l, _i, _i, _vp, _vp]),
+    "qtip_plain_to_kernel_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "qtip_kernel_to_plain_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "qtip_matvec_workspace_bytes": (_sz, [_i, _i, _i]),
     "qtip_decompress_matvec": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_decompress_matvec_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "qtip_decompress_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "qtip_decompress_gemm_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "qtip_linear_fused": (_i, [ctypes.POINTER(LinearDesc), _i, _i, _i, _i, _i, _vp]),
+    "qtip_linear_desc_layout": (_i, [ctypes.POINTER(ctypes.c_size_t), _i]),
     "qtip_decompress_matvec_plain": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "qtip_rht": (_i, [_vp, _i, _vp, _i, _l, _i, _vp, _i, _vp, _l, _vp, _i, _i, _f, _vp]),
     "qtip_rht_fused": (_i, [_vp, _i, _vp, _i, _l, _l, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _l, _vp, _i, _i, _f,
@@ -70,8 +74,21 @@ def load():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
+        check_desc_layout(lib)
         _lib = lib
     return _lib
+
+
+def check_desc_layout(lib):
+    """The ctypes mirror of qtip_linear_desc against the compiled struct (size and every field offset): a mirror that is
+    out of step would hand the kernels pointer bits as counts and limits."""
+    n = lib.qtip_linear_desc_layout(None, 0)
+    got = (ctypes.c_size_t * n)()
+    lib.qtip_linear_desc_layout(got, n)
+    want = [ctypes.sizeof(LinearDesc)] + [getattr(LinearDesc, name).offset for name, _ in LinearDesc._fields_]
+    if list(got) != want:
+        raise RuntimeError(f"qtip_linear_desc layout mismatch between {SO_PATH} and qtip_b200/_lib.py: library {list(got)}, "
+                           f"binding {want}")
 
 
 def check(status, what):

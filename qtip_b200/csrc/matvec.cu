@@ -41,6 +41,8 @@
 // Upstream counterpart: kernel_decompress_matvec, qtip-kernels/src/inference.cu:168-425.
 #include <mutex>
 
+#include <cstddef>
+
 #include "fwht.cuh"
 
 namespace qtip {
@@ -1159,6 +1161,24 @@ extern "C" int qtip_decompress_matvec_plain(float *out, const void *codes, const
         matvec_plain_kernel<QTIP_CODE_1MAD><<<p.grid, kPlainWarps * 32, smem, s>>>(out, c, xh, K, m, n, bs, p.kmax,
                                                                                  p.mode, ws);
     return check_launch();
+}
+
+// sizeof(qtip_linear_desc) followed by the byte offset of every field in declaration order: lets a foreign-language
+// mirror of the struct (ctypes, cgo, JNA ...) prove at start-up that it agrees with the compiled library.  A mirror
+// that is one field out of step turns a pointer's low bits into peer_max_polls or a count.
+extern "C" int qtip_linear_desc_layout(size_t *out, int capacity) {
+#define QTIP_F(f) offsetof(qtip_linear_desc, f)
+    const size_t v[] = {sizeof(qtip_linear_desc), QTIP_F(y), QTIP_F(codes), QTIP_F(tlut), QTIP_F(x), QTIP_F(workspace),
+                        QTIP_F(workspace_bytes), QTIP_F(in_raw), QTIP_F(residual), QTIP_F(residual_out), QTIP_F(norm_weight),
+                        QTIP_F(gate), QTIP_F(sign_in), QTIP_F(in_scale), QTIP_F(eps), QTIP_F(out), QTIP_F(out_dtype),
+                        QTIP_F(sign_out), QTIP_F(out_scale), QTIP_F(in_y), QTIP_F(in_y_sign), QTIP_F(in_y_scale),
+                        QTIP_F(peer_count), QTIP_F(peer_y), QTIP_F(peer_seq), QTIP_F(peer_status), QTIP_F(peer_max_polls),
+                        QTIP_F(signal_count), QTIP_F(signal_y), QTIP_F(signal_seq)};
+#undef QTIP_F
+    const int count = (int)(sizeof(v) / sizeof(v[0]));
+    if (out)
+        for (int i = 0; i < count && i < capacity; i++) out[i] = v[i];
+    return count;
 }
 
 extern "C" int qtip_linear_fused(const qtip_linear_desc *descs, int count, int K, int m, int n, int bs, void *stream) {

@@ -164,6 +164,53 @@ def decode_plain(codes, code, K, m, n, tlut=None, out=None):
     return out
 
 
+def pack_trellis(states, K, V, check=True):
+    """Trellis states (tiles, 256/V) int32 -> packed plain-layout words (tiles, 16K) int16 (pack_trellis upstream).
+    check=True counts the state pairs that violate the overlap condition upstream asserts and raises if any."""
+    _require_cuda(states)
+    states = states.to(torch.int32).contiguous()
+    tiles = states.shape[0]
+    if states.shape[1] * V != 256:
+        raise RuntimeError(f"states must be (tiles, {256 // V}) for V = {V}")
+    words = torch.empty(tiles, 16 * K, dtype=torch.int16, device=states.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=states.device) if check else None
+    with torch.cuda.device(states.device):
+        st = _lib.load().qtip_pack_trellis(words.data_ptr(), states.data_ptr(), tiles, K, V,
+                                           None if bad is None else bad.data_ptr(), _stream())
+    _lib.check(st, "qtip_pack_trellis")
+    global launch_count
+    launch_count += 1
+    if check and int(bad.item()):
+        raise RuntimeError(f"pack_trellis: {int(bad.item())} consecutive state pairs do not overlap (not a trellis walk)")
+    return words
+
+
+def plain_to_kernel_layout(words, K, m, n):
+    """Plain-layout words (tiles, 16K) -> kernel layout (same shape / dtype); lib/algo/finetune.py:196-201 upstream."""
+    _require_cuda(words)
+    words = words.contiguous()
+    out = torch.empty_like(words)
+    with torch.cuda.device(words.device):
+        st = _lib.load().qtip_plain_to_kernel_layout(out.data_ptr(), words.data_ptr(), K, m, n, _stream())
+    _lib.check(st, "qtip_plain_to_kernel_layout")
+    global launch_count
+    launch_count += 1
+    return out
+
+
+def kernel_to_plain_layout(codes, K, m, n):
+    """Inverse of plain_to_kernel_layout (lib/utils/kernel_decompress.py:19-24 upstream)."""
+    _require_cuda(codes)
+    codes = codes.contiguous()
+    out = torch.empty_like(codes)
+    with torch.cuda.device(codes.device):
+        st = _lib.load().qtip_kernel_to_plain_layout(out.data_ptr(), codes.data_ptr(), K, m, n, _stream())
+    _lib.check(st, "qtip_kernel_to_plain_layout")
+    global launch_count
+    launch_count += 1
+    return out
+
+
 def decompress_matvec(codes, x, tlut, K, m, n, out=None, workspace=None):
     """out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T, HYB kernel layout, bs <= 8."""
     _require_cuda(codes, x, tlut)

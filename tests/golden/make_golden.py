@@ -5,6 +5,7 @@
 Every array saved here is either a seeded input or the output of an upstream function on it:
   decode_kernel.npz  lib/utils/kernel_decompress.py decode_compressed          (HYB, kernel layout)
   decode_plain.npz   lib/codebook/bitshift.py unpack_trellis + get_hatW        (3INST, 1MAD, HYB; plain layout)
+  pack_trellis.npz   lib/codebook/bitshift.py pack_trellis on tail-biting and on open trellis walks
   hadamard.npz       lib/utils/matmul_had.py matmul_hadU / matmul_hadUt
   layer.npz          lib/codebook/bitshift.py BitshiftLinear.forward (has_kernel=False, CPU)
   layer4096.npz      the same forward on the 4096x4096, 2-bit configuration with inputs drawn by
@@ -62,6 +63,25 @@ def main():
             out[f"states_{mode}_K{K}"] = st.numpy().astype(np.uint16)
             out[f"W_{mode}_K{K}"] = W.numpy()  # fp32 for 3inst / 1mad, fp16 for HYB
     np.savez_compressed(os.path.join(HERE, "decode_plain.npz"), **out)
+
+    # ---- pack_trellis (own generator: the draws of the other fixtures stay as they were) ---------------
+    g2 = torch.Generator().manual_seed(20240612)
+    out = {}
+    for K in (2, 3, 4):
+        for mode, V in (("3inst", 1), ("quantlut_sym", 2)):
+            kw = dict(tlut_bits=9, tlut=tlut) if V == 2 else dict(tlut_bits=0)
+            cb = B.bitshift_codebook(L=16, K=K, V=V, decode_mode=mode, **kw)
+            T, kv = 256 // V, K * V
+            codes = torch.randint(0, 65536, (6, 16 * K), generator=g2).to(torch.uint16)
+            closed = cb.unpack_trellis(codes.view(torch.int16), 256).to(torch.int64)
+            walk = torch.zeros(4, T, dtype=torch.int64)
+            walk[:, 0] = torch.randint(0, 65536, (4,), generator=g2)
+            for i in range(1, T):
+                walk[:, i] = ((walk[:, i - 1] << kv) & 0xFFFF) | torch.randint(0, 1 << kv, (4,), generator=g2)
+            states = torch.cat([closed, walk])
+            out[f"states_V{V}_K{K}"] = states.numpy().astype(np.uint16)
+            out[f"packed_V{V}_K{K}"] = cb.pack_trellis(states).numpy()
+    np.savez_compressed(os.path.join(HERE, "pack_trellis.npz"), **out)
 
     # ---- Hadamard ---------------------------------------------------------------------------------
     out = {}

@@ -37,6 +37,35 @@ def test_every_declared_symbol_is_exported():
         assert hasattr(lib, name), f"{name} declared in include/qtip_b200.h but not exported"
 
 
+def test_linear_desc_mirror_matches_the_compiled_struct():
+    lib = ctypes.CDLL(_lib.SO_PATH)
+    lib.qtip_linear_desc_layout.restype = ctypes.c_int
+    lib.qtip_linear_desc_layout.argtypes = [ctypes.POINTER(ctypes.c_size_t), ctypes.c_int]
+    n = lib.qtip_linear_desc_layout(None, 0)
+    assert n == 1 + len(_lib.LinearDesc._fields_)
+    got = (ctypes.c_size_t * n)()
+    assert lib.qtip_linear_desc_layout(got, n) == n
+    assert got[0] == ctypes.sizeof(_lib.LinearDesc)
+    for k, (name, _) in enumerate(_lib.LinearDesc._fields_):
+        assert got[1 + k] == getattr(_lib.LinearDesc, name).offset, name
+    # the header declares the fields in the same order as the binding
+    text = open(os.path.join(ROOT, "include", "qtip_b200.h")).read()
+    body = re.search(r"typedef struct qtip_linear_desc \{(.*?)\} qtip_linear_desc;", text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = [re.search(r"(\w+)(\[\d+\])?\s*$", d.strip()).group(1) for d in body.split(";") if d.strip()]
+    assert names == [name for name, _ in _lib.LinearDesc._fields_]
+    # a mirror that is out of step is refused at load time
+    class Short(ctypes.Structure):
+        _fields_ = _lib.LinearDesc._fields_[:-1]
+    orig = _lib.LinearDesc
+    try:
+        _lib.LinearDesc = Short
+        with pytest.raises(RuntimeError, match="layout mismatch"):
+            _lib.check_desc_layout(lib)
+    finally:
+        _lib.LinearDesc = orig
+
+
 def test_status_strings():
     lib = _lib.load()
     assert lib.qtip_status_string(0) == b"ok"

@@ -47,6 +47,61 @@ def test_decode_hyb_vs_oracle(K, m, n):
     assert np.array_equal(u16(W), u16(C.decode_kernel(lay["codes"], m, n, K, lay["tlut"])))
 
 
+# ---- producers of the packed formats: bit exact ---------------------------------------------------------
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("V", [1, 2])
+def test_pack_trellis_golden(golden, K, V):
+    g = golden("pack_trellis")
+    states = torch.from_numpy(g[f"states_V{V}_K{K}"].astype(np.int32)).to(DEV)
+    words = ops.pack_trellis(states, K, V)
+    assert np.array_equal(u16(words), g[f"packed_V{V}_K{K}"])
+    bad = states.clone()
+    bad[1, 7] ^= 0x8000          # the top bit overlaps with the previous state only
+    with pytest.raises(RuntimeError, match="1 consecutive state pairs"):
+        ops.pack_trellis(bad, K, V)
+    # check=False packs whatever it is given, like the arithmetic upstream without its assert
+    ops.pack_trellis(bad, K, V, check=False)
+
+
+@pytest.mark.parametrize("K,V,m,n", [(2, 2, 4096, 4096), (3, 2, 1024, 2048), (4, 2, 256, 512), (2, 1, 2048, 1024), (4, 1, 512, 512)])
+def test_pack_trellis_round_trip(K, V, m, n):
+    """pack(unpack(words)) == words on uniform code words (every 256*K-bit stream is a tail-biting walk), and against
+    the numpy restatement on a sample of the tiles."""
+    rng = np.random.default_rng(77 + K + V)
+    codes = rng.integers(0, 65536, size=(m * n // 256, 16 * K), dtype=np.uint16)
+    states = O.states_plain_layout(codes, m, n, K, V)
+    words = ops.pack_trellis(torch.from_numpy(states.astype(np.int32)).to(DEV), K, V)
+    assert np.array_equal(u16(words), codes)
+    assert np.array_equal(O.pack_trellis(states[:64], K, V), codes[:64])
+
+
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("m,n", [(32, 64), (64, 96), (4096, 4096), (4096, 11008)])
+def test_layout_shuffle_vs_oracle(K, m, n):
+    rng = np.random.default_rng(5 + K)
+    plain = rng.integers(0, 65536, size=(m * n // 256, 16 * K), dtype=np.uint16)
+    kern = ops.plain_to_kernel_layout(dev(plain), K, m, n)
+    assert np.array_equal(u16(kern).reshape(-1), O.plain_words_to_kernel_layout(plain, m, n, K).reshape(-1))
+    back = ops.kernel_to_plain_layout(kern, K, m, n)
+    assert np.array_equal(u16(back), plain)
+    assert np.array_equal(u16(ops.kernel_to_plain_layout(dev(plain), K, m, n)).reshape(-1),
+                          O.kernel_layout_to_plain_words(plain, m, n, K).reshape(-1))
+
+
+def test_quantizer_tail_to_decoder():
+    """States -> pack_trellis -> kernel layout -> the fused decoder gives the plain-layout decode of the same states with
+    the elements moved by the kernel's sequence permutation (what lib/algo/finetune.py:188-201 hands to the kernels)."""
+    K, m, n = 2, 256, 512
+    lay = synth.make_layer(m, n, K, seed=31)
+    plain = O.kernel_layout_to_plain_words(lay["codes"], m, n, K)
+    states = O.states_plain_layout(plain, m, n, K, 2)
+    words = ops.pack_trellis(torch.from_numpy(states.astype(np.int32)).to(DEV), K, 2)
+    kern = ops.plain_to_kernel_layout(words, K, m, n)
+    assert np.array_equal(u16(kern).reshape(-1), lay["codes"].reshape(-1))
+    W = ops.decode_hyb(kern, dev(lay["tlut"]), K, m, n)
+    assert np.array_equal(u16(W), u16(C.decode_kernel(lay["codes"], m, n, K, lay["tlut"])))
+
+
 @pytest.mark.parametrize("K", [2, 3, 4])
 @pytest.mark.parametrize("mode", ["3inst", "1mad", "quantlut_sym"])
 def test_decode_plain_golden(golden, K, mode):

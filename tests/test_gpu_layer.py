@@ -146,6 +146,42 @@ def test_legacy_entry_point_and_graph_capture():
         fn(out, compressed, x.float(), codebook)
 
 
+@pytest.mark.parametrize("m,n,K", [(4096, 4096, 2), (11008, 4096, 3), (4096, 11008, 4)])
+def test_quip_lib_op_on_the_shim(m, n, K):
+    """The torch.library op of lib/codebook/__init__.py:68-92 upstream, dispatched on the GPU to this package installed as
+    `qtip_kernels`.  With QTIP_REFERENCE_ROOT pointing at a checkout the upstream file itself is imported, unmodified;
+    otherwise an op with the same schema and the same call into `qtip_kernels` is registered here."""
+    import os
+    import sys
+    import qtip_b200
+    qtip_b200.install_as_qtip_kernels()
+    root = os.environ.get("QTIP_REFERENCE_ROOT")
+    name = f"decompress_matvec_qtip_{m}_1_{n}_{K}"
+    if root and os.path.isdir(os.path.join(root, "lib", "codebook")):
+        if root not in sys.path:
+            sys.path.insert(0, root)
+        import lib.codebook  # noqa: F401  (registers quip_lib::*)
+        op = getattr(torch.ops.quip_lib, name)
+    else:
+        import qtip_kernels as qk            # resolves to the shim
+        ns = "qtip_b200_shim_test"
+        if not hasattr(getattr(torch.ops, ns), name):
+            torch.library.define(f"{ns}::{name}", "(Tensor compressed, Tensor x, Tensor codebook) -> Tensor")
+
+            @torch.library.impl(f"{ns}::{name}", "cuda")
+            def _impl(compressed, x, codebook):
+                out = torch.zeros((m, 1), dtype=torch.float32, device=x.device)
+                getattr(qk, f"decompress_matvec_16_9_{K}_1_{m}_1_{n}")(out, compressed.reshape(-1).view(torch.int32),
+                                                                       x.to(torch.float16).T, codebook.reshape(-1))
+                return out.T
+        op = getattr(getattr(torch.ops, ns), name)
+    lay = synth.make_layer(m, n, K, seed=19)
+    y = op(t16(lay["codes"]), torch.from_numpy(lay["x"]).to(DEV), torch.from_numpy(lay["tlut"]).to(DEV))
+    assert tuple(y.shape) == (1, m) and y.dtype == torch.float32
+    want = C.matvec_kernel(lay["codes"], m, n, K, lay["tlut"], lay["x"])
+    assert rel_l2(y.cpu().numpy(), want) < 2e-6
+
+
 @pytest.mark.parametrize("tp", [2, 4, 8])
 def test_tensor_parallel_shards_equal_unsharded_layer(tp):
     """Sum (row-parallel) / concatenation (column-parallel) of the per-rank results equals the unsharded

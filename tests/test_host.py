@@ -47,6 +47,35 @@ def test_legacy_kernel_names_resolve():
           torch.zeros(1024, dtype=torch.float16))
 
 
+def test_upstream_codebook_package_imports_on_the_shim():
+    """lib/codebook/__init__.py upstream, unmodified, registers its 61 quip_lib ops against this package installed as
+    `qtip_kernels`, and every kernel name it calls resolves (needs a checkout: QTIP_REFERENCE_ROOT)."""
+    import os
+    import subprocess
+    import sys
+    root = os.environ.get("QTIP_REFERENCE_ROOT")
+    if not root or not os.path.isdir(os.path.join(root, "lib", "codebook")):
+        pytest.skip("QTIP_REFERENCE_ROOT is not set to an upstream checkout")
+    code = (
+        "import sys, torch\n"
+        "import qtip_b200; qtip_b200.install_as_qtip_kernels()\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import lib.codebook as cb, qtip_kernels\n"
+        "assert len(cb.kernels) == 61\n"
+        "for m, n, k, r in cb.kernels:\n"
+        "    assert callable(getattr(qtip_kernels, f'decompress_matvec_16_9_{r}_1_{m}_{n}_{k}'))\n"
+        "    op = getattr(torch.ops.quip_lib, f'decompress_matvec_qtip_{m}_{n}_{k}_{r}')\n"
+        "from torch._subclasses.fake_tensor import FakeTensorMode\n"
+        "with FakeTensorMode():\n"
+        "    y = torch.ops.quip_lib.decompress_matvec_qtip_4096_1_4096_2(torch.zeros(65536, 32, dtype=torch.int16),\n"
+        "        torch.zeros(1, 4096, dtype=torch.float16), torch.zeros(512, 2, dtype=torch.float16))\n"
+        "    assert tuple(y.shape) == (1, 4096)\n"
+        "print('shim ok')\n")
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=here, timeout=300)
+    assert r.returncode == 0 and "shim ok" in r.stdout, r.stderr[-2000:]
+
+
 def test_quantized_linear_state_dict_keys():
     q = QuantizedLinear(11008, 4096, 16, 16, 16, 2, 2, 9, 'quantlut_sym')
     sd = q.state_dict()

@@ -46,6 +46,21 @@ def test_decode_plain_layout_golden(golden, K, mode, V, code):
     assert np.array_equal(u16(C.decode_plain(codes, 32, 64, K, V, table)), u16(want16))
 
 
+@pytest.mark.parametrize("K", [2, 3, 4])
+@pytest.mark.parametrize("V", [1, 2])
+def test_pack_trellis_golden(golden, K, V):
+    g = golden("pack_trellis")
+    states = g[f"states_V{V}_K{K}"]
+    assert np.array_equal(O.pack_trellis(states, K, V), g[f"packed_V{V}_K{K}"])
+    # the first six walks of the fixture bite their tail: unpacking the words gives the states back
+    back = O.states_plain_layout(g[f"packed_V{V}_K{K}"][:6], 16, 96, K, V)
+    assert np.array_equal(back, states[:6])
+    bad = states.copy()
+    bad[1, 7] ^= 0x8000
+    with pytest.raises(ValueError):
+        O.pack_trellis(bad, K, V)
+
+
 def test_c_tables_match_numpy():
     assert np.array_equal(u16(C.code_table(1)), u16(O.decode_3inst_table()))
     assert np.array_equal(u16(C.code_table(2)), u16(O.decode_1mad_table().astype(np.float16)))
