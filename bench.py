@@ -476,10 +476,13 @@ def main():
     ap.add_argument("--impl", default="qtip_b200", choices=["qtip_b200", "reference"])
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded in lockstep (<= 8; the batch rides in the matvec launches); value counts all of them")
-    ap.add_argument("--fuse-qkv", action="store_true",
-                    help="q||k||v and gate||up as ONE matrix each (12288x4096, 22016x4096 at the 7B shape), the layout "
-                         "upstream's published 188 tok/s was measured with")
+    ap.add_argument("--separate-qkv", action="store_true",
+                    help="keep q, k, v and gate, up as separate matrices (three / two problems in one launch).  The default on "
+                         "one GPU at batch 1 is q||k||v and gate||up as ONE matrix each (12288x4096, 22016x4096 at the 7B shape), "
+                         "the layout upstream's published 188 tok/s was measured with; tensor-parallel and batched runs "
+                         "always use separate matrices")
     args = ap.parse_args()
+    args.fuse_qkv = not args.separate_qkv and args.gpus == 1 and args.batch == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -50,7 +50,7 @@ int qtip_version(void);
 
 /* HYB code, kernel layout.  Replaces decode_compressed (lib/utils/kernel_decompress.py:4-55) and
  * BitshiftLinear.get_hatW_kernel (lib/codebook/bitshift.py:383-387); bit-exact with them.
- * codes: K*m*n/8 bytes, 16-byte aligned; tlut: 512x2 fp16; m, n multiples of 32; K in {2,3,4}. */
+ * codes: K*m*n/8 bytes, 16-byte aligned; W 16-byte aligned; tlut: 512x2 fp16; m, n multiples of 32; K in {2,3,4}. */
 int qtip_decode_hyb(void *W, const void *codes, const void *tlut, int K, int m, int n, void *stream);
 
 /* Plain layout, any of the three codes.  Replaces unpack_trellis + recons + get_hatW

@@ -13,15 +13,21 @@ namespace {
 
 constexpr int kDecodeThreads = 256;
 
+// Row stride of a warp's staging tile in 32-bit words: 16 data words + 4 of padding, so that the scattered 4-byte
+// stores of the eight fragment rows fall into distinct banks while rows stay 16-byte aligned for the read-back.
+constexpr int kStageStride = 20;
+
 template <int K>
 __global__ void __launch_bounds__(kDecodeThreads) decode_hyb_kernel(__half *__restrict__ W,
                                                                    const uint8_t *__restrict__ codes,
                                                                    const uint32_t *__restrict__ tlut, int m, int n) {
     __shared__ uint32_t lut[512];
+    __shared__ __align__(16) uint32_t stage_all[kDecodeThreads / 32][32 * kStageStride];
     for (int i = threadIdx.x; i < 512; i += blockDim.x) lut[i] = tlut[i];
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
+    uint32_t *stage = stage_all[threadIdx.x >> 5];
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int nb = n >> 5;
     const long blocks = (long)(m >> 5) * nb;
@@ -30,6 +36,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_hyb_kernel(__half *__re
         const int M = (int)(blk / nb), N = (int)(blk % nb);
         LaneCodes<K> own = load_lane_codes<K>(codes + blk * (128 * K) + lane * (4 * K));
         LaneCodes<K> nxt = shfl_next_lane<K>(own, lane);
+        // decode into the warp's 32 x 32 staging tile (fragment order -> row-major) ...
 #pragma unroll
         for (int t = 0; t < 4; t++) {
             const int ks = t >> 1, ms = t & 1;
@@ -40,11 +47,18 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_hyb_kernel(__half *__re
                 const int c = q >> 1, d = q & 1;
                 uint32_t h = hyb_hash(st[q]);
                 uint32_t w = lut[(h >> 6) & 511u] ^ (h & 0x8000u);
-                size_t row = (size_t)32 * M + 16 * ms + 8 * d + a;
-                size_t col = (size_t)32 * N + 16 * ks + 8 * c + 2 * b;
-                *reinterpret_cast<uint32_t *>(W + row * n + col) = w;
+                stage[(16 * ms + 8 * d + a) * kStageStride + 8 * ks + 4 * c + b] = w;     // cols 16ks + 8c + 2b, +1
             }
         }
+        __syncwarp();
+        // ... and write it out as 64-byte row segments: one 16-byte store per lane covers 8 rows x 64 bytes
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = 8 * i + a;
+            const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kStageStride + 4 * b);
+            *reinterpret_cast<uint4 *>(W + ((size_t)32 * M + r) * n + (size_t)32 * N + 8 * b) = v;
+        }
+        __syncwarp();
     }
 }
 
@@ -119,7 +133,7 @@ using namespace qtip;
 extern "C" int qtip_decode_hyb(void *W, const void *codes, const void *tlut, int K, int m, int n, void *stream) {
     if (!W || !codes || !tlut || K < 2 || K > 4) return QTIP_ERR_BAD_ARG;
     if (m <= 0 || n <= 0 || (m & 31) || (n & 31)) return QTIP_ERR_BAD_SHAPE;
-    if (!aligned(codes, 16) || !aligned(W, 4) || !aligned(tlut, 4)) return QTIP_ERR_ALIGNMENT;
+    if (!aligned(codes, 16) || !aligned(W, 16) || !aligned(tlut, 4)) return QTIP_ERR_ALIGNMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int grid = decode_grid((long)(m >> 5) * (n >> 5));
     auto *Wh = static_cast<__half *>(W);

@@ -201,7 +201,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (brow >= bs) return make_uint4(0u, 0u, 0u, 0u);
             return *reinterpret_cast<const uint4 *>(x + (size_t)brow * n + c0 + step * kStageCols + c * 8);
         };
-        LaneCodes<K> own_next = {};
+        // codes: two steps of this warp ahead (the warp's steps are kGroups apart), x: one step ahead
+        LaneCodes<K> own_next = {}, own_next2 = {};
         uint4 xv0_next = make_uint4(0u, 0u, 0u, 0u), xv1_next = xv0_next;
         // plain layout (V = 1 codes): tile (tile row, tile column) = 16K words at ((row/16)*(n/16) + col/16)*16K; this
         // lane decodes row pr of each of the warp's four tiles, columns 8*ph .. 8*ph+7
@@ -212,12 +213,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (has0) xv0_next = load_x(group, tid8);
             if (has1) xv1_next = load_x(group, tid8 + 256);
         }
+        if constexpr (kHyb)
+            if (group + kGroups < nsteps) own_next2 = load_lane_codes<K>(src + (size_t)(group + kGroups) * 2 * kBlockBytes);
+        // HYB: byte offsets of this lane's four 16-byte chunks (ks, c) inside a 128-byte row of the A tile, swizzled by
+        // the row (row % 8 == a for every row this lane writes); rows (ms, d) are 1024-byte groups apart
+        uint32_t chunk_off[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) chunk_off[j] = (((uint32_t)(4 * cb + j)) ^ (uint32_t)a) << 4;
         for (int step = group; step < nsteps; step += kGroups) {
             const int s = step % kStages, round = step / kStages;
             const LaneCodes<K> own = own_next;
             const uint4 xv0 = xv0_next, xv1 = xv1_next;
+            own_next = own_next2;
+            if constexpr (kHyb)
+                if (step + 2 * kGroups < nsteps) own_next2 = load_lane_codes<K>(src + (size_t)(step + 2 * kGroups) * 2 * kBlockBytes);
             if (step + kGroups < nsteps) {
-                if constexpr (kHyb) own_next = load_lane_codes<K>(src + (size_t)(step + kGroups) * 2 * kBlockBytes);
                 if (has0) xv0_next = load_x(step + kGroups, tid8);
                 if (has1) xv1_next = load_x(step + kGroups, tid8 + 256);
             }
@@ -251,20 +261,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             }
             if constexpr (kHyb) {
                 const uint32_t ast = a_base + s * kAStageBytes + row_off;
+                uint32_t dst4[4];                       // chunk (ks, c) of this lane's row with ms = 0, d = 0
+#pragma unroll
+                for (int j = 0; j < 4; j++) dst4[j] = ast + chunk_off[j];
 #pragma unroll
                 for (int tt = 0; tt < 4; tt++) {
                     const int ks = tt >> 1, ms = tt & 1;
                     uint32_t st[4];
-                    lane_states<K>(lane_slice<K>(own, tt), lane_slice<K>(nxt, tt), st);
+                    tile_states<K>(own, nxt, tt, st);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const int c = q >> 1, d = q & 1;
-                        const uint32_t h = hyb_hash(st[q]);
-                        uint32_t w;
-                        asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lut_lane + ((h & 0xFFC0u) << 1)));
-                        const uint32_t chunk = (uint32_t)(4 * cb + 2 * ks + c);
-                        const uint32_t dst = ast + (uint32_t)(2 * ms + d) * 1024u + ((chunk ^ (uint32_t)a) << 4);
-                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(w) : "memory");
+                        const uint32_t w = hyb_lookup(st[q], lut_lane);
+                        // the row offset is a compile-time constant after unrolling: register + immediate addressing
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst4[2 * ks + c] + (uint32_t)(2 * ms + d) * 1024u), "r"(w) : "memory");
                     }
                 }
             } else {

@@ -229,53 +229,6 @@ __device__ __forceinline__ void finish_segment(float (&acc)[2][4], float *red, S
     asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
 }
 
-// The four states of tile tt (= ks*2 + ms) of a lane, from the lane's own words and those of lane+1.
-// Only the low 16 bits of each st[q] are meaningful (the hash ignores the rest), which saves the
-// masks and, for the state that already sits in the low half of a word, the shift.  Shifts are
-// funnel shifts of (own : next) so no 64-bit value is ever formed.
-template <int K>
-__device__ __forceinline__ void tile_states(const LaneCodes<K> &own, const LaneCodes<K> &nxt, int tt, uint32_t (&st)[4]) {
-    if constexpr (K == 2) {
-        // word ks holds slice(ms=1) << 16 | slice(ms=0); state q = low 16 bits of (own slice << 4q | next slice >> (16-4q))
-        const uint32_t w = own.w[tt >> 1], nw = nxt.w[tt >> 1];
-        if ((tt & 1) == 0) {
-            const uint32_t lo = nw << 16;  // next slice in the top half
-            st[0] = w; st[1] = __funnelshift_l(lo, w, 4); st[2] = __funnelshift_l(lo, w, 8); st[3] = __funnelshift_l(lo, w, 12);
-        } else {
-            const uint32_t hi = w >> 16;   // nw already has the next slice in its top half
-            st[0] = hi; st[1] = __funnelshift_l(nw, hi, 4); st[2] = __funnelshift_l(nw, hi, 8); st[3] = __funnelshift_l(nw, hi, 12);
-        }
-    } else if constexpr (K == 3) {
-        // 24-bit slices at byte offset 3*tt.  S: own slice in the low 24 bits (junk above is shifted
-        // out); N: next slice with its top 16 bits in the top half of the register.
-        uint32_t S, N;
-        if (tt == 0) { S = own.w[0]; N = nxt.w[0] << 8; }
-        else if (tt == 1) { S = __funnelshift_r(own.w[0], own.w[1], 24); N = __funnelshift_r(nxt.w[0], nxt.w[1], 16); }
-        else if (tt == 2) { S = __funnelshift_r(own.w[1], own.w[2], 16); N = __funnelshift_r(nxt.w[1], nxt.w[2], 8); }
-        else { S = own.w[2] >> 8; N = nxt.w[2]; }
-        // window bit 47 = first bit of S; state q = window bits [47-6q .. 32-6q]
-        st[0] = S >> 8; st[1] = S >> 2; st[2] = __funnelshift_l(N, S, 4); st[3] = __funnelshift_l(N, S, 10);
-    } else {
-        const uint32_t S = own.w[tt], N = nxt.w[tt];
-        st[0] = S >> 16; st[1] = S >> 8; st[2] = S; st[3] = __funnelshift_l(N, S, 8);
-    }
-}
-
-// One HYB lookup: h = t*t + t; entry = h bits 15..6 (bit 15 = sign flip of the first weight, folded
-// into the table); 128 bytes per entry, the lane's copy selected by lut_lane.  Two of the four
-// instructions are integer multiply-adds, which issue at full rate; logic ops are half rate.
-__device__ __forceinline__ uint32_t hyb_lookup(uint32_t t, uint32_t lut_lane) {
-    uint32_t w;
-    asm("{\n\t.reg .b32 h, a;\n\t"
-        "mad.lo.u32 h, %1, %1, %1;\n\t"
-        "and.b32 h, h, 0xFFC0;\n\t"
-        "mad.lo.u32 a, h, 2, %2;\n\t"
-        "ld.shared.u32 %0, [a];\n\t}"
-        : "=r"(w)
-        : "r"(t), "r"(lut_lane));
-    return w;
-}
-
 // 16 states of one lane -> four A fragments -> four MMAs (2 k-subtiles x 2 m-subtiles).
 template <int K>
 __device__ __forceinline__ void decode_block(const LaneCodes<K> &own, const LaneCodes<K> &nxt, const uint32_t (&xb)[4],
