@@ -60,6 +60,19 @@ int qtip_decode_hyb(void *W, const void *codes, const void *tlut, int K, int m, 
 int qtip_decode_plain(void *W, const void *codes, int code, const void *tlut, int K, int m, int n, void *stream);
 
 /* --------------------------------------------------------------------------------------------
+ * Measurement support (no counterpart in the reference): issue rates of the instruction classes the decoders are
+ * made of, measured on the current device.  The decode kernels are bound by instruction issue rather than by HBM,
+ * so these rates, not the memory bandwidth, set their ceiling.
+ * qtip_measure_pipe_rates fills cycles[i], i < qtip_pipe_rate_count(), with the cycles one warp-instruction of class i
+ * (qtip_pipe_rate_name(i)) costs per SM sub-partition when every sub-partition runs threads_per_cta/128 warps of
+ * independent chains; the two "decode sequence" classes are counted per trellis state.  Host pointer; the call
+ * allocates and frees its own device scratch and synchronises the device (not for use inside a serving loop).
+ * ------------------------------------------------------------------------------------------ */
+int qtip_pipe_rate_count(void);
+const char *qtip_pipe_rate_name(int i);
+int qtip_measure_pipe_rates(double *cycles, int count, int threads_per_cta);
+
+/* --------------------------------------------------------------------------------------------
  * Producers of the packed formats (the quantizer side of the format; pure bit / byte movement, bit-exact).
  * ------------------------------------------------------------------------------------------ */
 

@@ -32,6 +32,9 @@ SIGNATURES = {
     "qtip_version": (_i, []),
     "qtip_decode_hyb": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "qtip_decode_plain": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "qtip_pipe_rate_count": (_i, []),
+    "qtip_pipe_rate_name": (ctypes.c_char_p, [_i]),
+    "qtip_measure_pipe_rates": (_i, [ctypes.POINTER(ctypes.c_double), _i, _i]),
     "qtip_pack_trellis": (_i, [_vp, _vp, _l, _i, _i, _vp, _vp]),
     "qtip_plain_to_kernel_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "qtip_kernel_to_plain_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),

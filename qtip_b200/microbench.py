@@ -122,6 +122,21 @@ def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0, mid=F
     return e0.elapsed_time(e1) * 1e3 / (replays * launches)
 
 
+def pipe_rates():
+    """The ceiling of the decode kernels: what the integer pipes, the shared-memory gather and the legacy MMA issue per clock."""
+    import ctypes
+    from . import _lib
+    lib = _lib.load()
+    n = lib.qtip_pipe_rate_count()
+    for threads in (1024, 512):
+        buf = (ctypes.c_double * n)()
+        _lib.check(lib.qtip_measure_pipe_rates(buf, n, threads), "qtip_measure_pipe_rates")
+        for i in range(n):
+            name = lib.qtip_pipe_rate_name(i).decode()
+            unit = "state" if "per state" in name else "warp-instruction"
+            print(f"{threads // 32:2d} warps/SM  {name:55s} {buf[i]:6.2f} cycles per {unit} per sub-partition", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mlp-mid", default="", help="comma-separated widths: time qtip_mlp_mid")
@@ -132,9 +147,15 @@ def main():
     ap.add_argument("--code", default="hyb", choices=["hyb", "3inst", "1mad"])
     ap.add_argument("--plain-launches", type=int, default=0)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--pipes", action="store_true",
+                    help="issue rates of the instruction classes the decoders are made of (cycles per warp-instruction per "
+                         "SM sub-partition), with 32 and 16 warps per SM")
     ap.add_argument("--plain-matvec", action="store_true",
                     help="compute codes, batch <= 8: time the mma.sync matvec instead of the tcgen05 kernel")
     args = ap.parse_args()
+    if args.pipes:
+        pipe_rates()
+        return
     global _PLAIN_MATVEC
     _PLAIN_MATVEC = args.plain_matvec
     peak = None

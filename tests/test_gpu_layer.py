@@ -457,6 +457,18 @@ def test_linear_fused_peer_sum_and_signal():
     ops.linear_fused([got], K, m, n, 1)
     torch.cuda.synchronize()
     assert int(status) == 1
+    # a launch AFTER a recorded run-out does not wait again: every stamp stale (a lost GPU), default limits, and the
+    # launch still returns at once (the 200 ms time bound is never reached) with the status word left set
+    for v in vecs:
+        v[:, 1] = 3
+    got.pop("peer_max_polls")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    ops.linear_fused([got], K, m, n, 1)
+    e1.record()
+    torch.cuda.synchronize()
+    assert e0.elapsed_time(e1) < 50.0, "a launch after a recorded time-out polled again"
+    assert int(status) != 0
 
 
 def test_quip_lib_op_under_graph_capture():
