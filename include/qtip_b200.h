@@ -83,6 +83,19 @@ int qtip_measure_pipe_rates(double *cycles, int count, int threads_per_cta);
  * overlap by 16 - K*V bits (upstream asserts this, :306-309); the words are written either way. */
 int qtip_pack_trellis(void *words, const int *states, long tiles, int K, int V, unsigned *violations, void *stream);
 
+/* bitshift_codebook.quantize (lib/codebook/bitshift.py:283-292; viterbi / update / quantize_seq :203-281): the Viterbi
+ * quantizer over the L = 16 bitshift trellis with tail-biting.  X: N sequences of T fp16 values (upstream: the rows of
+ * the (N, td_x*td_y) matrix handed to quantize(); T = 256 for 16x16 tiles).  states: (N, T/V) int32, the states of the
+ * minimum-squared-error walk whose last state ends with the bits its first state begins with - identical to the states
+ * upstream's implementation returns (same fp32 arithmetic, same tie-breaking), ready for qtip_pack_trellis.
+ * final_cost (optional): the walk's total squared error per sequence.  code: QTIP_CODE_HYB (V = 2; tlut = 512 x 2 FP32,
+ * the table the quantizer holds in fp32) or QTIP_CODE_3INST / QTIP_CODE_1MAD (V = 1, tlut ignored).  K in {2,3,4};
+ * T a multiple of 2V, 4V <= T <= 1024.  workspace: qtip_viterbi_workspace_bytes() bytes of device memory
+ * (back-pointers; no initialisation needed). */
+size_t qtip_viterbi_workspace_bytes(int code, int K, int T, long N);
+int qtip_viterbi_quantize(int *states, float *final_cost, const void *X, long N, int T, int code, int K, const float *tlut,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* The byte shuffle from the plain layout to the kernel layout for L = 16, V = 2, 16x16 tiles
  * (lib/algo/finetune.py:196-201) and its inverse (lib/utils/kernel_decompress.py:19-24).  Both buffers hold
  * K*m*n/8 bytes and must not alias; m, n multiples of 32. */

@@ -120,3 +120,16 @@ def layer_forward(x, codes, m, n, K, tlut, SU, SV, had_left=None, had_right=None
                            1 if hl is None else hl.shape[0], _p(hr), 1 if hr is None else hr.shape[0],
                            rcp, tp, _p(y))
     return y
+
+
+def viterbi_quantize(X, K, V, recons):
+    """bitshift_codebook.quantize (lib/codebook/bitshift.py:283-292): X (N, T) fp16 sequences, recons (V, 65536) fp32
+    (upstream's recons_state) -> (states (N, T/V) int32, final path cost (N,) fp32)."""
+    X = np.ascontiguousarray(X, dtype=np.float16)
+    N, T = X.shape
+    recons = np.ascontiguousarray(recons, dtype=np.float32).reshape(V, 65536)
+    states = np.empty((N, T // V), dtype=np.int32)
+    cost = np.empty(N, dtype=np.float32)
+    lib().qo_viterbi_quantize(_p(X.view(np.uint16)), ctypes.c_long(N), ctypes.c_int(T), ctypes.c_int(K), ctypes.c_int(V),
+                              _p(recons), _p(states), _p(cost))
+    return states, cost

@@ -104,6 +104,19 @@ def main():
             check(f"pack_trellis open walk {mode} K={K}",
                   np.array_equal(cb.pack_trellis(walk).numpy(), O.pack_trellis(walk.numpy(), K, V)))
 
+    # --- the Viterbi quantizer (tail-biting), C restatement against upstream's quantize() --------------------------
+    import c_oracle as C_
+    tlut32 = torch.randn(512, 2, generator=g)
+    for mode, K, V, code in (("quantlut_sym", 2, 2, O.CODE_HYB), ("quantlut_sym", 4, 2, O.CODE_HYB), ("3inst", 2, 1, O.CODE_3INST),
+                             ("1mad", 3, 1, O.CODE_1MAD)):
+        kw = dict(tlut_bits=9, tlut=tlut32) if V == 2 else dict(tlut_bits=0)
+        cb = bs_mod.bitshift_codebook(L=16, K=K, V=V, decode_mode=mode, **kw)
+        X = torch.randn(3, 256, generator=g)
+        _, st = cb.quantize(X)
+        check(f"recons table {mode}", np.array_equal(cb.recons_state.numpy().reshape(V, -1).view(np.uint32), O.recons_table(code, tlut32.numpy()).view(np.uint32)))
+        got, _ = C_.viterbi_quantize(X.half().numpy(), K, V, O.recons_table(code, tlut32.numpy()))
+        check(f"viterbi quantize {mode} K={K}", np.array_equal(st.numpy(), got))
+
     # --- Hadamard ---------------------------------------------------------------------------------
     for n in (128, 4096, 11008, 6656, 14336):
         x = torch.randn(2, n, generator=g)

@@ -285,3 +285,83 @@ void qo_layer_forward(const float *x, int bs, const uint8_t *codes, int m, int n
     free(xs);
     free(xh);
 }
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Viterbi quantizer over the bitshift trellis with tail-biting: bitshift_codebook.quantize
+ * (lib/codebook/bitshift.py:283-292) = quantize_seq / viterbi / update (:203-281), in upstream's own formulation:
+ * a cost per state (2^16 floats), per step the minimum over the 2^(KV) predecessors of each group of 2^(KV) states
+ * that share them (first minimal index wins, as torch.min), the squared error of the state's reconstruction added,
+ * back-pointers per group, back-trace from the first minimal final state.
+ * recons: [V][65536] fp32 (upstream's recons_state); X: N sequences of T fp16 values; states: N x T/V.
+ * Arithmetic follows the eager torch ops in fp32: (r - x), square, sum over V, + best.  Built with -ffp-contract=off.
+ * ------------------------------------------------------------------------------------------------------------------ */
+static inline float seq_err(const float *recons, int V, uint32_t s, const float *x) {
+    const float d0 = recons[s] - x[0];
+    float e = d0 * d0;
+    if (V == 2) {
+        const float d1 = recons[65536 + s] - x[1];
+        e = e + d1 * d1;
+    }
+    return e;
+}
+
+static void viterbi_pass(const float *x, int S, int KV, int V, const float *recons, int has_overlap, uint32_t overlap,
+                         int32_t *out, float *cost, float *cost2, uint16_t *from, float *final_cost) {
+    const uint32_t D = 1u << KV, G = 65536u >> KV;
+    for (uint32_t s = 0; s < 65536; s++) cost[s] = seq_err(recons, V, s, x);
+    if (has_overlap)   /* viterbi :225-231: only states whose top 16-KV bits equal `overlap` may start the walk */
+        for (uint32_t s = 0; s < 65536; s++)
+            if ((s >> KV) != overlap) cost[s] = INFINITY;
+    for (int i = 1; i < S; i++) {
+        uint16_t *fr = from + (size_t)i * G;
+        for (uint32_t g = 0; g < G; g++) {
+            float best = cost[g];
+            uint32_t bd = 0;
+            for (uint32_t d = 1; d < D; d++) {
+                const float c = cost[g + d * G];
+                if (c < best) { best = c; bd = d; }
+            }
+            fr[g] = (uint16_t)(g + bd * G);
+            for (uint32_t j = 0; j < D; j++) {
+                const uint32_t s = g * D + j;
+                cost2[s] = seq_err(recons, V, s, x + (size_t)i * V) + best;
+            }
+        }
+        float *t = cost; cost = cost2; cost2 = t;
+    }
+    if (has_overlap)   /* :244-249: the last state's low 16-KV bits must equal `overlap` */
+        for (uint32_t s = 0; s < 65536; s++)
+            if ((s & (G - 1)) != overlap) cost[s] = INFINITY;
+    uint32_t arg = 0;
+    for (uint32_t s = 1; s < 65536; s++)
+        if (cost[s] < cost[arg]) arg = s;
+    if (final_cost) *final_cost = cost[arg];
+    out[S - 1] = (int32_t)arg;
+    for (int i = S - 1; i > 0; i--) out[i - 1] = from[(size_t)i * G + ((uint32_t)out[i] >> KV)];
+}
+
+void qo_viterbi_quantize(const uint16_t *X, long N, int T, int K, int V, const float *recons, int32_t *states,
+                         float *final_cost) {
+    qo_init();
+    const int KV = K * V, S = T / V;
+    const uint32_t G = 65536u >> KV;
+#pragma omp parallel
+    {
+        float *cost = (float *)malloc(65536 * sizeof(float)), *cost2 = (float *)malloc(65536 * sizeof(float));
+        uint16_t *from = (uint16_t *)malloc((size_t)S * G * sizeof(uint16_t));
+        float *x = (float *)malloc((size_t)T * sizeof(float)), *xr = (float *)malloc((size_t)T * sizeof(float));
+        int32_t *tmp = (int32_t *)malloc((size_t)S * sizeof(int32_t));
+#pragma omp for schedule(dynamic, 1)
+        for (long b = 0; b < N; b++) {
+            for (int t = 0; t < T; t++) x[t] = g_h2f[X[b * T + t]];
+            /* quantize :286-289: first pass on the sequence rolled by T/(2V)*V, free ends; the state it finds where the
+             * original sequence starts gives the overlap bits both ends of the second pass must agree on */
+            const int roll = T / (2 * V) * V;
+            for (int t = 0; t < T; t++) xr[(t + roll) % T] = x[t];
+            viterbi_pass(xr, S, KV, V, recons, 0, 0u, tmp, cost, cost2, from, NULL);
+            const uint32_t overlap = (uint32_t)tmp[T / (2 * V)] >> KV;
+            viterbi_pass(x, S, KV, V, recons, 1, overlap, states + b * S, cost, cost2, from, final_cost ? final_cost + b : NULL);
+        }
+        free(cost); free(cost2); free(from); free(x); free(xr); free(tmp);
+    }
+}

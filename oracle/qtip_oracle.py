@@ -138,6 +138,20 @@ def states_plain_layout(codes, m, n, K, V):
     return st.astype(np.uint16)
 
 
+def recons_table(code, tlut32=None):
+    """Upstream's recons_state as the quantizer holds it: (V, 65536) fp32.  HYB: quantlut_sym on the fp32 table
+    (lib/codebook/bitshift.py:72-80); 3INST: the fp16-exact values as fp32 (:43-60); 1MAD: the fp32 values (:17-26)."""
+    if code == CODE_HYB:
+        s = np.arange(1 << L_BITS, dtype=np.uint64)
+        h = (s * (s + 1)) & 0xFFFF
+        t = np.asarray(tlut32, dtype=np.float32).reshape(512, 2)[(h >> 6) & 511].copy()
+        t[:, 0] *= (1 - 2 * ((h >> 15) & 1).astype(np.float32))
+        return np.ascontiguousarray(t.T)
+    if code == CODE_3INST:
+        return decode_3inst_table().astype(np.float32).reshape(1, -1)
+    return decode_1mad_table().astype(np.float32).reshape(1, -1)
+
+
 def pack_trellis(states, K, V):
     """Trellis states [tiles][256/V] -> plain-layout words [tiles][16*K] uint16.
 

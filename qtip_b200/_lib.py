@@ -35,6 +35,8 @@ SIGNATURES = {
     "qtip_pipe_rate_count": (_i, []),
     "qtip_pipe_rate_name": (ctypes.c_char_p, [_i]),
     "qtip_measure_pipe_rates": (_i, [ctypes.POINTER(ctypes.c_double), _i, _i]),
+    "qtip_viterbi_workspace_bytes": (_sz, [_i, _i, _i, _l]),
+    "qtip_viterbi_quantize": (_i, [_vp, _vp, _vp, _l, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "qtip_pack_trellis": (_i, [_vp, _vp, _l, _i, _i, _vp, _vp]),
     "qtip_plain_to_kernel_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "qtip_kernel_to_plain_layout": (_i, [_vp, _vp, _i, _i, _i, _vp]),

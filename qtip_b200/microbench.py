@@ -122,6 +122,29 @@ def time_rht(n, rows=1, device="cuda:0", replays=20, launches=32, plain=0, mid=F
     return e0.elapsed_time(e1) * 1e3 / (replays * launches)
 
 
+def time_viterbi(N):
+    """Sequences per second of qtip_viterbi_quantize (CUDA events around one call after a warm-up call)."""
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(11)
+    X = torch.randn(N, 256, generator=g, device=dev).half()
+    tlut = torch.randn(512, 2, generator=g, device=dev)
+    for mode, Ks in (("quantlut_sym", (2, 3, 4)), ("3inst", (2, 3, 4)), ("1mad", (2,))):
+        for K in Ks:
+            ops.viterbi_quantize(X[:256], mode, K, tlut=tlut)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _, cost = ops.viterbi_quantize(X, mode, K, tlut=tlut, return_cost=True)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            V = 2 if mode == "quantlut_sym" else 1
+            evals = 2.0 * N * (256 // V) * 65536          # candidate evaluations: two passes, 2^16 per step
+            print(f"viterbi {mode} K={K}: {N} sequences in {ms:8.2f} ms = {N / ms * 1e3:9.0f} sequences/s, "
+                  f"{evals / ms / 1e9:6.2f} T candidate evaluations/s, mean squared error {float(cost.sum()) / (N * 256):.4f}",
+                  flush=True)
+
+
 def pipe_rates():
     """The ceiling of the decode kernels: what the integer pipes, the shared-memory gather and the legacy MMA issue per clock."""
     import ctypes
@@ -147,6 +170,8 @@ def main():
     ap.add_argument("--code", default="hyb", choices=["hyb", "3inst", "1mad"])
     ap.add_argument("--plain-launches", type=int, default=0)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--viterbi", type=int, default=0, metavar="N",
+                    help="time the tail-biting Viterbi quantizer on N sequences of 256 values for every code / bitrate")
     ap.add_argument("--pipes", action="store_true",
                     help="issue rates of the instruction classes the decoders are made of (cycles per warp-instruction per "
                          "SM sub-partition), with 32 and 16 warps per SM")
@@ -155,6 +180,9 @@ def main():
     args = ap.parse_args()
     if args.pipes:
         pipe_rates()
+        return
+    if args.viterbi:
+        time_viterbi(args.viterbi)
         return
     global _PLAIN_MATVEC
     _PLAIN_MATVEC = args.plain_matvec

@@ -164,6 +164,36 @@ def decode_plain(codes, code, K, m, n, tlut=None, out=None):
     return out
 
 
+def viterbi_quantize(X, mode, K, tlut=None, return_cost=False):
+    """bitshift_codebook.quantize upstream (lib/codebook/bitshift.py:283-292): X (N, T) -> trellis states (N, T/V) int32 of
+    the tail-biting minimum-squared-error walk (X is rounded to fp16 first, as upstream does).  mode: 'quantlut_sym'
+    (tlut: 512 x 2, used in fp32), '3inst' or '1mad'."""
+    _require_cuda(X)
+    code = CODE_IDS[mode]
+    V = 2 if code == CODE_HYB else 1
+    X = X.to(torch.float16).contiguous()
+    N, T = X.shape
+    tl = None
+    if code == CODE_HYB:
+        if tlut is None:
+            raise RuntimeError("the HYB code needs its 512 x 2 table")
+        tl = tlut.to(device=X.device, dtype=torch.float32).contiguous()
+        if tl.numel() != 1024:
+            raise RuntimeError("tlut must hold 512 x 2 values")
+    lib = _lib.load()
+    need = lib.qtip_viterbi_workspace_bytes(code, K, T, N)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=X.device)
+    states = torch.empty(N, T // V, dtype=torch.int32, device=X.device)
+    cost = torch.empty(N, dtype=torch.float32, device=X.device)
+    with torch.cuda.device(X.device):
+        st = lib.qtip_viterbi_quantize(states.data_ptr(), cost.data_ptr(), X.data_ptr(), N, T, code, K,
+                                       None if tl is None else tl.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
+    _lib.check(st, "qtip_viterbi_quantize")
+    global launch_count
+    launch_count += 1
+    return (states, cost) if return_cost else states
+
+
 def pack_trellis(states, K, V, check=True):
     """Trellis states (tiles, 256/V) int32 -> packed plain-layout words (tiles, 16K) int16 (pack_trellis upstream).
     check=True counts the state pairs that violate the overlap condition upstream asserts and raises if any."""

@@ -6,6 +6,7 @@ Every array saved here is either a seeded input or the output of an upstream fun
   decode_kernel.npz  lib/utils/kernel_decompress.py decode_compressed          (HYB, kernel layout)
   decode_plain.npz   lib/codebook/bitshift.py unpack_trellis + get_hatW        (3INST, 1MAD, HYB; plain layout)
   pack_trellis.npz   lib/codebook/bitshift.py pack_trellis on tail-biting and on open trellis walks
+  viterbi.npz        lib/codebook/bitshift.py bitshift_codebook.quantize (the tail-biting Viterbi quantizer) on a few sequences
   hadamard.npz       lib/utils/matmul_had.py matmul_hadU / matmul_hadUt
   layer.npz          lib/codebook/bitshift.py BitshiftLinear.forward (has_kernel=False, CPU)
   layer4096.npz      the same forward on the 4096x4096, 2-bit configuration with inputs drawn by
@@ -82,6 +83,22 @@ def main():
             out[f"states_V{V}_K{K}"] = states.numpy().astype(np.uint16)
             out[f"packed_V{V}_K{K}"] = cb.pack_trellis(states).numpy()
     np.savez_compressed(os.path.join(HERE, "pack_trellis.npz"), **out)
+
+    # ---- Viterbi quantizer (own generator) ----------------------------------------------------------------
+    g3 = torch.Generator().manual_seed(20240613)
+    tlut32 = torch.randn(512, 2, generator=g3)              # the quantizer holds its table in fp32
+    out = {"tlut32": tlut32.numpy()}
+    for mode, K, V, N in (("quantlut_sym", 2, 2, 6), ("quantlut_sym", 3, 2, 3), ("quantlut_sym", 4, 2, 3),
+                          ("3inst", 2, 1, 3), ("1mad", 2, 1, 3), ("3inst", 3, 1, 2), ("1mad", 4, 1, 2)):
+        kw = dict(tlut_bits=9, tlut=tlut32) if V == 2 else dict(tlut_bits=0)
+        cb = B.bitshift_codebook(L=16, K=K, V=V, decode_mode=mode, **kw)
+        X = torch.randn(N, 256, generator=g3)
+        X[0, :8] = 0.0                                       # a flat stretch: ties between equally good predecessors
+        hatX, st = cb.quantize(X)
+        out[f"X_{mode}_K{K}"] = X.half().numpy()
+        out[f"states_{mode}_K{K}"] = st.numpy().astype(np.uint16)
+        out[f"hatX_{mode}_K{K}"] = hatX.numpy().astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "viterbi.npz"), **out)
 
     # ---- Hadamard ---------------------------------------------------------------------------------
     out = {}

@@ -63,6 +63,67 @@ def test_pack_trellis_golden(golden, K, V):
     ops.pack_trellis(bad, K, V, check=False)
 
 
+VITERBI_CASES = [("quantlut_sym", 2, 2), ("quantlut_sym", 3, 2), ("quantlut_sym", 4, 2), ("3inst", 2, 1), ("1mad", 2, 1),
+                 ("3inst", 3, 1), ("1mad", 4, 1)]
+
+
+@pytest.mark.parametrize("mode,K,V", VITERBI_CASES)
+def test_viterbi_quantize_golden(golden, mode, K, V):
+    """The tail-biting Viterbi quantizer returns the very states upstream's bitshift_codebook.quantize returned."""
+    g = golden("viterbi")
+    X = torch.from_numpy(g[f"X_{mode}_K{K}"]).to(DEV)
+    states = ops.viterbi_quantize(X, mode, K, tlut=torch.from_numpy(g["tlut32"]))
+    assert np.array_equal(states.cpu().numpy().astype(np.uint16), g[f"states_{mode}_K{K}"])
+
+
+@pytest.mark.parametrize("mode,K,V,N", [("quantlut_sym", 2, 2, 300), ("quantlut_sym", 3, 2, 40), ("quantlut_sym", 4, 2, 40),
+                                        ("3inst", 2, 1, 24), ("1mad", 3, 1, 24), ("3inst", 4, 1, 24)])
+def test_viterbi_quantize_vs_oracle(mode, K, V, N):
+    """More sequences than CTAs can hold at once (the grid-stride loop), scaled inputs, against the C restatement of
+    upstream's formulation (full cost vector per step); bit-exact states and final costs."""
+    rng = np.random.default_rng(40 + K + V)
+    code = ops.CODE_IDS[mode]
+    tlut32 = (rng.standard_normal((512, 2)) * 0.97).astype(np.float32)
+    X = (rng.standard_normal((N, 256)) * rng.uniform(0.2, 3.0, size=(N, 1))).astype(np.float16)
+    X[1] = 0                                                    # all candidates tie on a constant sequence
+    want, want_cost = C.viterbi_quantize(X, K, V, O.recons_table(code, tlut32))
+    got, cost = ops.viterbi_quantize(torch.from_numpy(X).to(DEV), mode, K, tlut=torch.from_numpy(tlut32), return_cost=True)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(cost.cpu().numpy().view(np.uint32), want_cost.view(np.uint32))
+
+
+def test_viterbi_quantize_to_decoder():
+    """The quantizer's tail on the GPU, end to end: sequences -> Viterbi states -> pack_trellis -> kernel layout -> fused
+    decoder.  4096 sequences (a 1024 x 1024 matrix of 16x16 tiles); the table is fp16-representable so that the decoder
+    (fp16 table) reproduces the quantizer's reconstruction exactly.  Checks that every walk bites its tail (pack_trellis
+    counts violations), that the decoded matrix is the reconstruction the quantizer minimised over, and that the
+    reported cost is its squared error."""
+    K, m, n = 2, 1024, 1024
+    rng = np.random.default_rng(9)
+    tl16 = rng.standard_normal((512, 2)).astype(np.float16)
+    W = rng.standard_normal((m, n)).astype(np.float32)
+    # 16x16 tiles as sequences, row-major inside the tile (lib/algo/finetune.py:188-194 hands these rows to the quantizer)
+    seqs = W.reshape(m // 16, 16, n // 16, 16).transpose(0, 2, 1, 3).reshape(-1, 256)
+    Xd = torch.from_numpy(seqs).to(DEV)
+    states, cost = ops.viterbi_quantize(Xd, "quantlut_sym", K, tlut=torch.from_numpy(tl16.astype(np.float32)), return_cost=True)
+    words = ops.pack_trellis(states, K, 2)                  # raises if a walk does not overlap / bite its tail
+    assert np.array_equal(O.states_plain_layout(u16(words), m, n, K, 2), states.cpu().numpy().astype(np.uint16))
+    hat = ops.decode_plain(words, "quantlut_sym", K, m, n, tlut=dev(tl16)).float().cpu().numpy()
+    x16 = seqs.astype(np.float16).astype(np.float64).reshape(m // 16, n // 16, 16, 16).transpose(0, 2, 1, 3).reshape(m, n)
+    err_tiles = ((hat.astype(np.float64) - x16) ** 2).reshape(m // 16, 16, n // 16, 16).sum(axis=(1, 3)).reshape(-1)
+    assert np.allclose(cost.cpu().numpy(), err_tiles, rtol=1e-5)
+    # 2 bits per weight on N(0,1) data: the trellis code gets close to the rate-distortion bound (0.0625); a scalar
+    # quantizer is at 0.118
+    assert 0.06 < err_tiles.sum() / (m * n) < 0.085
+    # a handful of sequences against the oracle
+    want, _ = C.viterbi_quantize(seqs[:16].astype(np.float16), K, 2, O.recons_table(O.CODE_HYB, tl16.astype(np.float32)))
+    assert np.array_equal(states[:16].cpu().numpy(), want)
+    # the same codes through the kernel layout and the fused decoder
+    kern = ops.plain_to_kernel_layout(words, K, m, n)
+    Wk = ops.decode_hyb(kern, dev(tl16), K, m, n)
+    assert np.array_equal(u16(Wk), u16(C.decode_kernel(u16(kern), m, n, K, tl16)))
+
+
 @pytest.mark.parametrize("K,V,m,n", [(2, 2, 4096, 4096), (3, 2, 1024, 2048), (4, 2, 256, 512), (2, 1, 2048, 1024), (4, 1, 512, 512)])
 def test_pack_trellis_round_trip(K, V, m, n):
     """pack(unpack(words)) == words on uniform code words (every 256*K-bit stream is a tail-biting walk), and against

@@ -61,6 +61,29 @@ def test_pack_trellis_golden(golden, K, V):
         O.pack_trellis(bad, K, V)
 
 
+VITERBI_CASES = [("quantlut_sym", 2, 2), ("quantlut_sym", 3, 2), ("quantlut_sym", 4, 2), ("3inst", 2, 1), ("1mad", 2, 1),
+                 ("3inst", 3, 1), ("1mad", 4, 1)]
+
+
+@pytest.mark.parametrize("mode,K,V", VITERBI_CASES)
+def test_viterbi_quantize_golden(golden, mode, K, V):
+    """The C restatement of the tail-biting Viterbi quantizer returns the states upstream's quantize() returned."""
+    g = golden("viterbi")
+    code = {"quantlut_sym": O.CODE_HYB, "3inst": O.CODE_3INST, "1mad": O.CODE_1MAD}[mode]
+    recons = O.recons_table(code, g["tlut32"])
+    X = g[f"X_{mode}_K{K}"]
+    states, cost = C.viterbi_quantize(X, K, V, recons)
+    assert np.array_equal(states.astype(np.uint16), g[f"states_{mode}_K{K}"])
+    # upstream's hatX is the reconstruction of those states, and the reported cost is its squared error
+    hat = recons[:, states].transpose(1, 2, 0).reshape(X.shape)
+    assert np.array_equal(hat, g[f"hatX_{mode}_K{K}"])
+    err = ((hat.astype(np.float64) - X.astype(np.float64)) ** 2).sum(axis=1)
+    assert np.allclose(cost, err, rtol=1e-5)
+    # the walks bite their tail: packing raises on a broken overlap, unpacking the words gives the states back
+    words = O.pack_trellis(states, K, V)
+    assert np.array_equal(O.states_plain_layout(words, 16, 16 * len(X), K, V), states.astype(np.uint16))
+
+
 def test_c_tables_match_numpy():
     assert np.array_equal(u16(C.code_table(1)), u16(O.decode_3inst_table()))
     assert np.array_equal(u16(C.code_table(2)), u16(O.decode_1mad_table().astype(np.float16)))
