@@ -90,7 +90,7 @@ int qtip_pack_trellis(void *words, const int *states, long tiles, int K, int V, 
  * upstream's implementation returns (same fp32 arithmetic, same tie-breaking), ready for qtip_pack_trellis.
  * final_cost (optional): the walk's total squared error per sequence.  code: QTIP_CODE_HYB (V = 2; tlut = 512 x 2 FP32,
  * the table the quantizer holds in fp32) or QTIP_CODE_3INST / QTIP_CODE_1MAD (V = 1, tlut ignored).  K in {2,3,4};
- * T a multiple of 2V, 4V <= T <= 1024.  workspace: qtip_viterbi_workspace_bytes() bytes of device memory
+ * T a multiple of 2V, 4V <= T <= 1024 and T*K >= 16 (a tail-biting walk needs at least 16 stream bits).  workspace: qtip_viterbi_workspace_bytes() bytes of device memory
  * (back-pointers; no initialisation needed). */
 size_t qtip_viterbi_workspace_bytes(int code, int K, int T, long N);
 int qtip_viterbi_quantize(int *states, float *final_cost, const void *X, long N, int T, int code, int K, const float *tlut,

@@ -228,7 +228,8 @@ extern "C" int qtip_viterbi_quantize(int *states, float *final_cost, const void 
     if (code != QTIP_CODE_HYB && code != QTIP_CODE_3INST && code != QTIP_CODE_1MAD) return QTIP_ERR_BAD_ARG;
     if (code == QTIP_CODE_HYB && !tlut) return QTIP_ERR_BAD_ARG;
     const int V = code == QTIP_CODE_HYB ? 2 : 1;
-    if (T < 4 * V || T > kMaxT || (T % (2 * V))) return QTIP_ERR_BAD_SHAPE;
+    // a tail-biting walk needs at least L = 16 stream bits (T*K): shorter sequences have no walk whose ends overlap
+    if (T < 4 * V || T * K < 16 || T > kMaxT || (T % (2 * V))) return QTIP_ERR_BAD_SHAPE;
     if (!aligned(states, 4) || !aligned(X, 2) || (tlut && !aligned(tlut, 8)) || (final_cost && !aligned(final_cost, 4)))
         return QTIP_ERR_ALIGNMENT;
     if (!workspace || workspace_bytes < qtip_viterbi_workspace_bytes(code, K, T, N)) return QTIP_ERR_WORKSPACE;

@@ -97,6 +97,28 @@ def test_argument_validation_without_device():
     assert lib.qtip_rht(p, 0, p, 0, 1, 344, None, 0, None, 344, None, 172, 0, 1.0, None) == _lib.ERR_BAD_ARG
     assert lib.qtip_rht(p, 3, p, 0, 1, 64, None, 0, None, 64, None, 1, 0, 1.0, None) == _lib.ERR_BAD_ARG
     assert lib.qtip_rht(p, 0, p, 0, 0, 64, None, 0, None, 64, None, 1, 0, 1.0, None) == _lib.OK  # zero rows: nothing to do
+    # producers of the packed formats
+    assert lib.qtip_pack_trellis(p, p, 0, 2, 2, None, None) == _lib.ERR_BAD_ARG          # no tiles
+    assert lib.qtip_pack_trellis(p, p, 4, 2, 3, None, None) == _lib.ERR_BAD_ARG          # V is 1 or 2
+    assert lib.qtip_pack_trellis(p, p + 2, 4, 2, 2, None, None) == _lib.ERR_ALIGNMENT
+    assert lib.qtip_plain_to_kernel_layout(p, p, 2, 32, 32, None) == _lib.ERR_BAD_ARG     # in place
+    assert lib.qtip_plain_to_kernel_layout(p, p + 2048, 2, 48, 32, None) == _lib.ERR_BAD_SHAPE
+    assert lib.qtip_kernel_to_plain_layout(p, p + 2048, 5, 32, 32, None) == _lib.ERR_BAD_ARG
+    need = lib.qtip_viterbi_workspace_bytes(_lib.CODE_HYB, 2, 256, 4)
+    assert need == 4 * 128 * 4096
+    assert lib.qtip_viterbi_workspace_bytes(_lib.CODE_3INST, 2, 256, 1000) == 148 * 256 * 16384 or \
+        lib.qtip_viterbi_workspace_bytes(_lib.CODE_3INST, 2, 256, 1000) % (256 * 16384) == 0
+    assert lib.qtip_viterbi_workspace_bytes(7, 2, 256, 4) == 0
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 256, _lib.CODE_HYB, 2, None, p, need, None) == _lib.ERR_BAD_ARG      # no table
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 256, _lib.CODE_HYB, 5, p, p, need, None) == _lib.ERR_BAD_ARG
+    assert lib.qtip_viterbi_quantize(p, None, p, 0, 256, _lib.CODE_3INST, 2, None, p, need, None) == _lib.ERR_BAD_ARG     # no sequences
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 6, _lib.CODE_HYB, 2, p, p, need, None) == _lib.ERR_BAD_SHAPE          # T % 2V
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 2048, _lib.CODE_HYB, 2, p, p, need, None) == _lib.ERR_BAD_SHAPE
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 4, _lib.CODE_3INST, 2, None, p, need, None) == _lib.ERR_BAD_SHAPE     # 8 stream bits
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 256, _lib.CODE_HYB, 2, p, p, need - 1, None) == _lib.ERR_WORKSPACE
+    assert lib.qtip_viterbi_quantize(p, None, p, 4, 256, _lib.CODE_HYB, 2, p + 4, p, need, None) == _lib.ERR_ALIGNMENT
+    assert lib.qtip_measure_pipe_rates(None, 10, 1024) == _lib.ERR_BAD_ARG
+    assert lib.qtip_pipe_rate_count() == 10 and lib.qtip_pipe_rate_name(0).startswith(b"IMAD") and lib.qtip_pipe_rate_name(99) == b""
 
 
 def test_missing_library_fails_loudly(monkeypatch):

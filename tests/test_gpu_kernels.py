@@ -92,6 +92,35 @@ def test_viterbi_quantize_vs_oracle(mode, K, V, N):
     assert np.array_equal(cost.cpu().numpy().view(np.uint32), want_cost.view(np.uint32))
 
 
+@pytest.mark.parametrize("mode,K,T,N", [("quantlut_sym", 2, 8, 3), ("quantlut_sym", 4, 16, 1), ("3inst", 2, 8, 2), ("1mad", 3, 64, 1),
+                                        ("quantlut_sym", 3, 1024, 2)])
+def test_viterbi_quantize_short_and_long_sequences(mode, K, T, N):
+    """Sequence lengths other than a 16x16 tile - the shortest the tail-biting construction allows (16 stream bits), a single
+    sequence, the longest the kernel takes (1024) - against the C restatement."""
+    rng = np.random.default_rng(T + K)
+    code = ops.CODE_IDS[mode]
+    V = 2 if mode == "quantlut_sym" else 1
+    tlut32 = rng.standard_normal((512, 2)).astype(np.float32)
+    X = rng.standard_normal((N, T)).astype(np.float16)
+    want, want_cost = C.viterbi_quantize(X, K, V, O.recons_table(code, tlut32))
+    got, cost = ops.viterbi_quantize(torch.from_numpy(X).to(DEV), mode, K, tlut=torch.from_numpy(tlut32), return_cost=True)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(cost.cpu().numpy().view(np.uint32), want_cost.view(np.uint32))
+
+
+def test_producers_smallest_shapes():
+    """One tile / one block: pack_trellis on a single tile, the layout shuffles on a single 32 x 32 block."""
+    rng = np.random.default_rng(3)
+    for K in (2, 3, 4):
+        plain = rng.integers(0, 65536, size=(4, 16 * K), dtype=np.uint16)
+        kern = ops.plain_to_kernel_layout(dev(plain), K, 32, 32)
+        assert np.array_equal(u16(kern).reshape(-1), O.plain_words_to_kernel_layout(plain, 32, 32, K).reshape(-1))
+        for V in (1, 2):
+            st = O.states_plain_layout(plain[:1], 16, 16, K, V)
+            words = ops.pack_trellis(torch.from_numpy(st.astype(np.int32)).to(DEV), K, V)
+            assert np.array_equal(u16(words), plain[:1])
+
+
 def test_viterbi_quantize_to_decoder():
     """The quantizer's tail on the GPU, end to end: sequences -> Viterbi states -> pack_trellis -> kernel layout -> fused
     decoder.  4096 sequences (a 1024 x 1024 matrix of 16x16 tiles); the table is fp16-representable so that the decoder
