@@ -40,13 +40,23 @@ WORKLOADS = {
 }
 
 
-def workload_config(workload, prompt, world):
+def workload_config(workload, prompt, world, fused=False):
     w = WORKLOADS[workload]
-    return {"workload": (f"{w['name']} shape ({w['n_layers']} layers, hidden {w['hidden']}, {w['n_heads']} heads, MLP {w['mlp']}, "
-                         f"vocab {w['vocab']}), every linear 2-bit HYB QTIP (L=16, Q=9, V=2, 16x16 tiles), "
-                         f"batch 1, {prompt}-token prompt, CUDA-graph decode"),
-            "l2": "each step streams all packed codes (1.6 GB for the 7B shape) and the lm_head, far larger than L2",
-            "parallelism": f"tp{world}"}
+    cfg = {"workload": (f"{w['name']} shape ({w['n_layers']} layers, hidden {w['hidden']}, {w['n_heads']} heads, MLP {w['mlp']}, "
+                        f"vocab {w['vocab']}), every linear 2-bit HYB QTIP (L=16, Q=9, V=2, 16x16 tiles), "
+                        f"batch 1, {prompt}-token prompt, CUDA-graph decode"),
+           "l2": "each step streams all packed codes (1.6 GB for the 7B shape) and the lm_head, far larger than L2",
+           "parallelism": f"tp{world}"}
+    if fused:
+        cfg["fused_matrices"] = "q||k||v and gate||up as one matrix each"
+    return cfg
+
+
+def use_fused_matrices(args):
+    """q||k||v and gate||up as ONE packed matrix each - the layers upstream's published decode speed was measured with -
+    is the default where it applies: the 7B shape (equal q / k / v widths) on one GPU at batch 1.  Both arms follow it."""
+    return (not args.separate_qkv and args.workload == "llama2-7b" and args.gpus == 1 and args.batch == 1
+            and int(os.environ.get("WORLD_SIZE", "1")) == 1)
 
 
 def metric_name(workload):
@@ -156,8 +166,9 @@ def run_reference(args):
         sample = f"2 of the {w['n_layers']} decoder layers per step, time scaled by {scale:g}; " + sample
         w["n_layers"] = layers_timed
     steps, warmup = args.steps, args.warmup
+    fused = use_fused_matrices(args)
     model = OracleLlama(_hadk_loader(), max_positions=args.prompt + warmup + steps + 8,
-                        weight_sets=4 if args.workload == "llama2-7b" else 1, **w)
+                        weight_sets=4 if args.workload == "llama2-7b" else 1, fuse_qkv=fused, **w)
     model.fill_cache(args.prompt)
     tok, per_step = 1, []
     for i in range(warmup + steps):
@@ -170,7 +181,7 @@ def run_reference(args):
     out = {"impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "tok/s", "n_gpus": args.gpus,
            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-           "dtype": "f16", "data": "synthetic", "config": workload_config(args.workload, args.prompt, args.gpus),
+           "dtype": "f16", "data": "synthetic", "config": workload_config(args.workload, args.prompt, args.gpus, fused),
            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)
@@ -179,7 +190,7 @@ def run_reference(args):
 def cpu_baseline_subprocess(args, steps=4, warmup=1):
     """The reference arm in a fresh process (no CUDA context, no second OpenMP runtime in the way), a few steps."""
     cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(steps), "--warmup", str(warmup),
-           "--prompt", str(args.prompt), "--workload", args.workload]
+           "--prompt", str(args.prompt), "--workload", args.workload] + (["--separate-qkv"] if args.separate_qkv else [])
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "OMP_NUM_THREADS")}
     try:
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
@@ -442,8 +453,7 @@ def run_gpu(args):
             "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": steps / (ms / 1e3) / PUBLISHED_TOK_S if seven_b else None,
             "dtype": "f16", "data": "synthetic",
-            "config": dict(workload_config(args.workload, args.prompt, world),
-                           **({"fused_matrices": "q||k||v and gate||up as one matrix each"} if args.fuse_qkv else {})),
+            "config": workload_config(args.workload, args.prompt, world, args.fuse_qkv),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "kernel": "matvec_hyb_kernel<K=2, staged x, 32 warps> (the instantiation every "
                          "launch of the decode graph uses), timed on this model's own weight sets, one launch per linear",
@@ -482,7 +492,7 @@ def main():
                          "the layout upstream's published 188 tok/s was measured with; tensor-parallel and batched runs "
                          "always use separate matrices")
     args = ap.parse_args()
-    args.fuse_qkv = not args.separate_qkv and args.gpus == 1 and args.batch == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1
+    args.fuse_qkv = use_fused_matrices(args)
     if args.impl == "reference":
         run_reference(args)
     else:

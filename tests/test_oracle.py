@@ -189,3 +189,27 @@ def test_c_matvec_matches_dense():
     a = C.matvec_kernel(lay["codes"], 128, 256, 3, lay["tlut"], lay["x"])
     b = C.matvec_dense(W, lay["x"])
     assert rel_l2(a, b) < 1e-5
+
+
+def test_cpu_decode_step_fused_matrices_equal_separate_linears():
+    """The CPU decode step of the benchmark's reference arm with q||k||v as ONE matrix (per-chunk output transforms, upstream's
+    rcp = 2 layout) gives what three separate linears over the same rows, table and signs give."""
+    import llama_oracle as LO
+    rng = np.random.default_rng(12)
+    hadk = lambda n: None  # noqa: E731  (powers of two only here)
+    m, n, K = 3 * 256, 512, 2
+    fused = LO._Lin(rng, m, n, K, hadk, chunks=3)
+    x = rng.standard_normal(n).astype(np.float32)
+    y = fused(x)
+    rows = m // 3
+    per = fused.codes.reshape(-1).size // 3
+    for c in range(3):
+        part = C.layer_forward(x, fused.codes.reshape(-1)[c * per:(c + 1) * per], rows, n, K, fused.tlut, fused.SU,
+                               fused.SV[c * rows:(c + 1) * rows], None, None)
+        assert np.array_equal(LO._f16(part.reshape(-1)), y[c * rows:(c + 1) * rows])
+    # and a whole step runs with fused matrices (tiny shape)
+    model = LO.OracleLlama(hadk, n_layers=2, hidden=256, n_heads=2, n_kv_heads=2, head_dim=128, mlp=512, vocab=64,
+                           max_positions=8, weight_sets=2, fuse_qkv=True)
+    model.fill_cache(3)
+    tok = model.step(5)
+    assert 0 <= tok < 64 and model.pos == 4
