@@ -247,6 +247,27 @@ def measure_matvec_roofline(model, torch, reps=5):
     return us, byts, launches
 
 
+def measure_issue_ceiling(torch, K, sm_mhz):
+    """What the SM's pipes allow the decode kernel at most, measured live: the per-state decode sequence (funnel shift,
+    multiply-add hash, mask, multiply-add address, lane-private shared load) as a pure loop on every SM, in cycles per
+    state per sub-partition; 16 states per 128*K-byte block on 4 sub-partitions -> GB/s over all SMs at the sampled clock."""
+    import ctypes
+    from qtip_b200 import _lib
+    lib = _lib.load()
+    n = lib.qtip_pipe_rate_count()
+    buf = (ctypes.c_double * n)()
+    if lib.qtip_measure_pipe_rates(buf, n, 1024) != 0:
+        return None
+    names = [lib.qtip_pipe_rate_name(i).decode() for i in range(n)]
+    cyc = next(buf[i] for i, nm in enumerate(names) if nm.startswith("decode sequence per state (shf"))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    gbs = 128 * K / (16 * cyc / 4) * sms * sm_mhz * 1e6 / 1e9
+    return {"cycles_per_state_per_subpartition": cyc, "gbs": gbs,
+            "what": "upper bound of any kernel that decodes one trellis state per table lookup: the decode instructions alone, "
+                    "no MMA, reduction or loop control (integer multiply-add, logic and shift instructions issue at one per "
+                    "two cycles per sub-partition on this part)"}
+
+
 def measure_layer_e2e(torch, K=2, m=4096, n=4096, reps=200):
     """One QTIP linear through the module the reference defines (QuantizedLinear.forward) with HOST buffers: per call
     the activation goes pinned host -> device, the layer runs (transform in, decode-matvec, transform out), the
@@ -466,6 +487,12 @@ def run_gpu(args):
             "clocks": clocks.summary(),
         }
         out.update(extra)
+        if world == 1:
+            ceil = measure_issue_ceiling(torch, 2, float(out["clocks"].get("sm_mhz") or 1965.0))
+            if ceil is not None:
+                ceil["frac_of_hbm_peak"] = ceil["gbs"] / peak
+                ceil["achieved_over_ceiling"] = achieved / ceil["gbs"]
+                out["roofline"]["issue_ceiling"] = ceil
     if out is not None:
         print(json.dumps(out), flush=True)
     if world > 1:
