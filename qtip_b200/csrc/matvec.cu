@@ -18,12 +18,14 @@
 // fragments in registers - HYB: h = s*(s+1), entry (h>>6)&1023 of a 1024-entry table (the 512-entry
 // LUT and its sign-flipped twin) kept as 32 lane-private copies in shared memory, so gathers never
 // conflict - and multiplies them with x held in the B fragment (column j of B = batch row j, so up
-// to 8 batch rows ride along for free).  fp32 accumulation in the MMA.  x is staged once per CTA
-// in shared memory in fragment order (one 16-byte load per block and lane).
+// to 8 batch rows share one decode).  fp32 accumulation in the MMA.  x is staged once per CTA
+// in shared memory in fragment order (one 16-byte load per block and lane) when it fits beside the
+// table; 8 rows of a wide layer do not, and are then read from L1/L2 per block (about 1.5x the time
+// of a single row).
 //
 // The kernel is instruction-issue bound, not HBM bound (about 5 instructions per state are
-// irreducible: shift, multiply-add hash, mask, multiply-add address, shared load; the integer pipes
-// run at half rate on this part).  The ring costs about one instruction per block because it is
+// irreducible: shift, multiply-add hash, mask, multiply-add address, shared load; multiply-add, logic
+// and shift instructions each issue once per two cycles per sub-partition on this part).  The ring costs about one instruction per block because it is
 // private to a warp: no producer warp, no CTA barrier, one bounded mbarrier wait per chunk.
 //
 // Reduction.  Warps of a CTA are summed through shared memory at the end of a segment.  When a
