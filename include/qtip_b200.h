@@ -121,7 +121,7 @@ size_t qtip_matvec_workspace_bytes(int m, int n, int bs);
 int qtip_decompress_matvec(float *out, const void *codes, const void *x, const void *tlut, int K, int m, int n,
                            int bs, void *workspace, size_t workspace_bytes, void *stream);
 
-/* Decompress-GEMM for batches up to 64 on the tcgen05 tensor cores (accumulator in tensor memory):
+/* Decompress-GEMM for batches up to 128 on the tcgen05 tensor cores (accumulator in tensor memory):
  * out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T, HYB code, kernel layout.  Replaces
  * BitshiftLinearKernelAG.forward (lib/codebook/bitshift.py:476-489: decode_compressed to a dense fp16
  * matrix in HBM, then a dense GEMM) without ever materialising the matrix.

@@ -113,7 +113,7 @@ class BitshiftLinear(nn.Module):
             else:
                 y = ops.decompress_matvec_plain(trellis, xh, self.cb.code, self.cb.K, m, n, workspace=self.workspace)
         elif self.has_kernel and ops.gemm_supported(m, n, bs):
-            # batches 9..64: decode inside the tensor-core GEMM, the dense matrix never exists
+            # batches 9..128: decode inside the tensor-core GEMM, the dense matrix never exists
             y = ops.decompress_gemm(trellis, xh, self.cb.tlut, self.cb.K, m, n)
         else:
             # anything else: decode once, dense fp16 GEMM (BitshiftLinearKernelAG upstream, bitshift.py:476-489)

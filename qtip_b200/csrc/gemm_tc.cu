@@ -1,4 +1,4 @@
-// Decompress-GEMM for batches 9..64 on the 5th-generation tensor cores (tcgen05 + TMEM).
+// Decompress-GEMM for batches 9..128 on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
 //   out (bs, m) fp32 = X (bs, n) fp16 @ decode(codes)^T        HYB code, kernel layout
 //
@@ -36,12 +36,12 @@ namespace {
 constexpr int kGroups = 3;                               // groups of 8 decode warps; a group fills one stage
 constexpr int kDecodeWarps = 8 * kGroups;
 constexpr int kGemmThreads = (kDecodeWarps + 1) * 32;   // + one control warp (TMEM allocation, MMA issue)
-constexpr int kStages = 4;
+constexpr int kStages = 4;                              // ring stages for batches up to 64; 3 for 65..128 (shared memory)
 constexpr int kRows = 128;                               // output rows per CTA
 constexpr int kStageCols = 64;                           // input columns per stage (128 bytes of fp16 per row)
 constexpr int kAStageBytes = kRows * kStageCols * 2;     // 16 KiB
 constexpr int kLut512Bytes = 1024 * 32 * 4;              // (512 entries + sign-flipped twins) x 32 lane-private copies
-constexpr int kMaxN = 64;
+constexpr int kMaxN = 128;
 constexpr unsigned kSpinLimit = 1u << 22;
 
 struct GemmCtrl {
@@ -124,11 +124,14 @@ __device__ __forceinline__ uint64_t plain_bits48(const uint16_t *__restrict__ wo
     return (v << (pos & 15)) >> 16;
 }
 
-template <int K, int CODE>
+// STAGES: ring depth, 4 for batches up to 64 (B tile <= 8 KiB), 3 above (16 KiB B tiles); a compile-time value so that
+// the ring arithmetic of the common case stays free of run-time divisions
+template <int K, int CODE, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     decompress_gemm_kernel(float *__restrict__ out, const uint8_t *__restrict__ codes, const __half *__restrict__ x,
                            const uint32_t *__restrict__ tlut, int m, int n, int bs, int npad, int splitk,
                            unsigned *__restrict__ status) {
+    constexpr int stages = STAGES;
     constexpr int kBlockBytes = 128 * K;
     constexpr bool kHyb = CODE == QTIP_CODE_HYB;
     extern __shared__ uint8_t smem_raw[];
@@ -137,16 +140,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint8_t *smem = smem_raw + (base - raw);
     const int b_stage_bytes = npad * 128;
     // layout: A stages | B stages | LUT | control
-    const uint32_t a_base = base, b_base = base + kStages * kAStageBytes;
-    uint32_t *lut = reinterpret_cast<uint32_t *>(smem + kStages * (kAStageBytes + b_stage_bytes));
-    GemmCtrl *ctl = reinterpret_cast<GemmCtrl *>(smem + kStages * (kAStageBytes + b_stage_bytes) + kLut512Bytes);
+    const uint32_t a_base = base, b_base = base + stages * kAStageBytes;
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem + stages * (kAStageBytes + b_stage_bytes));
+    GemmCtrl *ctl = reinterpret_cast<GemmCtrl *>(smem + stages * (kAStageBytes + b_stage_bytes) + kLut512Bytes);
     volatile int *abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tmem_cols = npad <= 32 ? 32 : 64;
+    const int tmem_cols = npad <= 32 ? 32 : (npad <= 64 ? 64 : 128);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < stages; s++) {
             mbar_init(smem_addr(&ctl->full[s]), 8);     // eight decode warps fill a stage
             mbar_init(smem_addr(&ctl->empty[s]), 1);    // one tcgen05.commit frees it
         }
@@ -192,18 +195,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // byte offset inside an A stage of this lane's element (ms, d, ks, c): row 32rb+16ms+8d+a, column 32cb+16ks+8c+2b
         const uint32_t row_off = (uint32_t)(4 * rb) * 1024u + (uint32_t)a * 128u + (uint32_t)b * 4u;
         const int tid8 = w8 * 32 + lane;                    // 0..255 within the stage's eight warps
-        // software pipeline: the codes and the x chunk(s) of the NEXT step of this warp are requested before
-        // the current step is decoded, so the global-memory latency is hidden behind a step of work
-        const int chunks = npad * 8;                        // 16-byte chunks of a B tile; <= 2 per thread
-        const bool has0 = tid8 < chunks, has1 = tid8 + 256 < chunks;
+        // The 64-column slice of x goes into the B tile of the stage: chunk ch of the tile = batch row ch >> 3, columns
+        // 8*(ch & 7) .. +7, rows beyond bs zero.  Batches up to 64 (at most two 16-byte chunks per thread): the chunks of
+        // the warp's NEXT step are requested into registers before the current step is decoded, so their latency hides
+        // behind a step of work.  Larger batches: asynchronous copies straight into the tile (no registers), awaited
+        // before the stage is handed over.
+        const int chunks = npad * 8;
+        constexpr bool small = STAGES == kStages;
+        const bool has0 = small && tid8 < chunks, has1 = small && tid8 + 256 < chunks;
         auto load_x = [&](int step, int ch) -> uint4 {
             const int brow = ch >> 3, c = ch & 7;
             if (brow >= bs) return make_uint4(0u, 0u, 0u, 0u);
             return *reinterpret_cast<const uint4 *>(x + (size_t)brow * n + c0 + step * kStageCols + c * 8);
         };
-        // codes: two steps of this warp ahead (the warp's steps are kGroups apart), x: one step ahead
-        LaneCodes<K> own_next = {}, own_next2 = {};
         uint4 xv0_next = make_uint4(0u, 0u, 0u, 0u), xv1_next = xv0_next;
+        // codes: two steps of this warp ahead (the warp's steps are kGroups apart)
+        LaneCodes<K> own_next = {}, own_next2 = {};
         // plain layout (V = 1 codes): tile (tile row, tile column) = 16K words at ((row/16)*(n/16) + col/16)*16K; this
         // lane decodes row pr of each of the warp's four tiles, columns 8*ph .. 8*ph+7
         const uint16_t *pcodes = reinterpret_cast<const uint16_t *>(codes);
@@ -220,17 +227,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t chunk_off[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) chunk_off[j] = (((uint32_t)(4 * cb + j)) ^ (uint32_t)a) << 4;
+        // ring position of this warp's step, kept incrementally (stages is a run-time value: no division in the loop)
+        int s = group % stages, round = group / stages;
         for (int step = group; step < nsteps; step += kGroups) {
-            const int s = step % kStages, round = step / kStages;
             const LaneCodes<K> own = own_next;
             const uint4 xv0 = xv0_next, xv1 = xv1_next;
             own_next = own_next2;
-            if constexpr (kHyb)
-                if (step + 2 * kGroups < nsteps) own_next2 = load_lane_codes<K>(src + (size_t)(step + 2 * kGroups) * 2 * kBlockBytes);
             if (step + kGroups < nsteps) {
                 if (has0) xv0_next = load_x(step + kGroups, tid8);
                 if (has1) xv1_next = load_x(step + kGroups, tid8 + 256);
             }
+            if constexpr (kHyb)
+                if (step + 2 * kGroups < nsteps) own_next2 = load_lane_codes<K>(src + (size_t)(step + 2 * kGroups) * 2 * kBlockBytes);
             // V = 1: the 44 bits this lane needs of each of its four tiles are requested before the wait for the stage
             uint64_t pbits[4];
             if constexpr (!kHyb) {
@@ -247,7 +255,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                 for (int i = 0; i < K; i++) nxt.w[i] = __shfl_sync(kFullMask, own.w[i], lane + 1);
             }
-            // B tile: rows = batch (zero beyond bs), 64 columns of x, 16-byte chunks swizzled by row % 8
+            // B tile: rows = batch (zero beyond bs), 64 columns of x, 16-byte chunks swizzled by row % 8; the copies run
+            // while this warp decodes and are awaited before the stage is handed to the MMA
             const uint32_t bst = b_base + s * b_stage_bytes;
             if (has0) {
                 const int brow = tid8 >> 3, c = tid8 & 7;
@@ -258,6 +267,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const int brow = (tid8 + 256) >> 3, c = tid8 & 7;
                 const uint32_t dst = bst + brow * 128 + ((c ^ (brow & 7)) << 4);
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(xv1.x), "r"(xv1.y), "r"(xv1.z), "r"(xv1.w) : "memory");
+            }
+            if constexpr (!small) {
+                for (int ch = tid8; ch < chunks; ch += 256) {
+                    const int brow = ch >> 3, c = ch & 7;
+                    const uint32_t dst = bst + brow * 128 + ((c ^ (brow & 7)) << 4);
+                    const bool live = brow < bs;
+                    const __half *srcx = live ? x + (size_t)brow * n + c0 + step * kStageCols + c * 8 : x;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(srcx), "r"(live ? 16 : 0) : "memory");
+                }
             }
             if constexpr (kHyb) {
                 const uint32_t ast = a_base + s * kAStageBytes + row_off;
@@ -297,16 +315,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
                 }
             }
+            if constexpr (!small) asm volatile("cp.async.wait_all;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&ctl->full[s]));
+            s += kGroups;
+            if (s >= stages) { s -= stages; round++; }      // kGroups <= stages: at most one wrap
         }
     } else if (lane == 0) {
         // ------------------------------------ MMA issue ---------------------------------------------------
         // instruction descriptor: D fp32, A/B fp16, both K-major, N = npad, M = 128
         const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+        int s = 0, round = 0;
         for (int step = 0; step < nsteps; step++) {
-            const int s = step % kStages, round = step / kStages;
             // a wait that gave up ends the issue loop: no further MMA is started, and the commit below still
             // covers everything issued so far
             if (!mbar_wait(smem_addr(&ctl->full[s]), round & 1, abort_flag, status, 2u)) break;
@@ -317,6 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             for (int kk = 0; kk < 4; kk++)   // 16 columns = 32 bytes further inside the 128-byte swizzled row
                 umma_f16(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (step | kk) != 0);
             umma_commit(smem_addr(&ctl->empty[s]));
+            if (++s == stages) { s = 0; round++; }
         }
         umma_commit(smem_addr(&ctl->done));
     }
@@ -357,10 +379,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
-template <int K, int CODE>
-int launch_gemm(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs, int npad,
-                int splitk, unsigned *status, cudaStream_t s) {
-    const int smem = 1024 + kStages * (kAStageBytes + npad * 128) + kLut512Bytes + 256;
+template <int K, int CODE, int STAGES>
+int launch_gemm_stages(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs, int npad,
+                       int splitk, unsigned *status, cudaStream_t s) {
+    const int smem = 1024 + STAGES * (kAStageBytes + npad * 128) + kLut512Bytes + 256;
     static bool attr_set[64] = {};
     static std::mutex attr_mutex;
     int dev = 0;
@@ -369,15 +391,23 @@ int launch_gemm(float *out, const uint8_t *codes, const __half *x, const uint32_
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         if (!attr_set[dev]) {
-            QTIP_CUDA_TRY(cudaFuncSetAttribute(decompress_gemm_kernel<K, CODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            QTIP_CUDA_TRY(cudaFuncSetAttribute(decompress_gemm_kernel<K, CODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                227 * 1024));
             attr_set[dev] = true;
         }
     }
     if (splitk > 1) QTIP_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)bs * m * sizeof(float), s));
-    decompress_gemm_kernel<K, CODE><<<dim3(m / kRows, splitk), kGemmThreads, smem, s>>>(out, codes, x, tlut, m, n, bs, npad,
-                                                                                        splitk, status);
+    decompress_gemm_kernel<K, CODE, STAGES><<<dim3(m / kRows, splitk), kGemmThreads, smem, s>>>(out, codes, x, tlut, m, n, bs,
+                                                                                                npad, splitk, status);
     return check_launch();
+}
+
+// four ring stages while the B tiles are small; batches above 64 (16 KiB per B tile) leave room for three
+template <int K, int CODE>
+int launch_gemm(float *out, const uint8_t *codes, const __half *x, const uint32_t *tlut, int m, int n, int bs, int npad,
+                int splitk, unsigned *status, cudaStream_t s) {
+    if (npad > 64) return launch_gemm_stages<K, CODE, 3>(out, codes, x, tlut, m, n, bs, npad, splitk, status, s);
+    return launch_gemm_stages<K, CODE, kStages>(out, codes, x, tlut, m, n, bs, npad, splitk, status, s);
 }
 
 template <int CODE>

@@ -30,7 +30,7 @@ def _sets(m, n, K, bs, code, device, min_bytes=400e6, max_sets=48):
 
 def _launch(lay, code, K, m, n, out, ws):
     if code == "hyb" and lay["x"].shape[0] > ops.MAX_MATVEC_BATCH:
-        ops.decompress_gemm(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out)      # tcgen05 path, batches 9..64
+        ops.decompress_gemm(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out)      # tcgen05 path, batches 9..128
     elif code == "hyb":
         ops.decompress_matvec(lay["codes"], lay["x"], lay["tlut"], K, m, n, out=out, workspace=ws)
     elif ops.gemm_plain_supported(m, n, lay["x"].shape[0]) and not _PLAIN_MATVEC:

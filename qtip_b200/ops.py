@@ -15,7 +15,7 @@ from ._lib import CODE_1MAD, CODE_3INST, CODE_HYB, F16, F32  # noqa: F401
 CODE_IDS = {"quantlut_sym": CODE_HYB, "hyb": CODE_HYB, "3inst": CODE_3INST, "1mad": CODE_1MAD}
 HAD_FACTORS = (172, 156, 140, 124, 116, 108, 60, 52, 36, 28, 20, 12)
 MAX_MATVEC_BATCH = 8
-MAX_GEMM_BATCH = 64
+MAX_GEMM_BATCH = 128
 launch_count = 0   # kernel launches issued through this module (bench.py reports it)
 
 
@@ -520,7 +520,7 @@ def gemm_status(device):
 
 
 def decompress_gemm(codes, x, tlut, K, m, n, out=None):
-    """out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T on the tcgen05 tensor cores, 1 <= bs <= 64."""
+    """out (bs, m) fp32 = x (bs, n) fp16 @ decode(codes)^T on the tcgen05 tensor cores, 1 <= bs <= 128."""
     _require_cuda(codes, x, tlut)
     if x.dtype != torch.float16:
         x = x.to(torch.float16)
@@ -541,7 +541,7 @@ def decompress_gemm(codes, x, tlut, K, m, n, out=None):
 
 
 def decompress_gemm_plain(codes, x, code, K, m, n, out=None):
-    """decompress_gemm for the 3INST / 1MAD compute codes (plain layout, V = 1), 1 <= bs <= 64."""
+    """decompress_gemm for the 3INST / 1MAD compute codes (plain layout, V = 1), 1 <= bs <= 128."""
     _require_cuda(codes, x)
     code = CODE_IDS.get(code, code)
     if x.dtype != torch.float16:

@@ -327,7 +327,7 @@ def test_rht_chunked_signs():
 # ---- tcgen05 decompress-GEMM ---------------------------------------------------------------------------------
 @pytest.mark.parametrize("K", [2, 3, 4])
 @pytest.mark.parametrize("m,n,bs", [(128, 64, 16), (256, 256, 9), (1024, 2048, 32), (8192, 8192, 16), (4096, 11008, 64),
-                                    (11008, 4096, 33)])
+                                    (11008, 4096, 33), (1024, 2048, 65), (4096, 4096, 128), (8192, 8192, 100)])
 def test_decompress_gemm(K, m, n, bs):
     """Tensor-core path against the dense product of the (bit-exact) decoded matrix, fp32 accumulation."""
     lay = synth.make_layer(m, n, K, seed=3300 + K, bs=bs)
@@ -346,7 +346,7 @@ def test_decompress_gemm(K, m, n, bs):
 @pytest.mark.gpu
 @pytest.mark.parametrize("code", [O.CODE_3INST, O.CODE_1MAD])
 @pytest.mark.parametrize("K,m,n,bs", [(2, 128, 64, 16), (2, 1024, 2048, 32), (3, 256, 256, 9), (4, 512, 1024, 64),
-                                      (2, 8192, 8192, 16)])
+                                      (2, 8192, 8192, 16), (2, 1024, 2048, 128), (3, 512, 1024, 72)])
 def test_decompress_gemm_plain_vs_oracle(code, K, m, n, bs):
     """Compute codes (V = 1, plain layout) on the tensor-core path against the CPU oracle: bit-exact decode
     (C.decode_plain with the oracle's state table) + dense product with fp32 accumulation."""
@@ -360,7 +360,7 @@ def test_decompress_gemm_plain_vs_oracle(code, K, m, n, bs):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("K,m,n,bs", [(2, 1024, 2048, 16), (4, 256, 256, 40)])
+@pytest.mark.parametrize("K,m,n,bs", [(2, 1024, 2048, 16), (4, 256, 256, 40), (3, 1024, 1024, 128), (2, 256, 512, 90)])
 def test_decompress_gemm_vs_oracle(K, m, n, bs):
     """The tensor-core path directly against the CPU oracle (decode of the kernel layout + dense product), with no
     CUDA kernel of this library on the reference side."""
