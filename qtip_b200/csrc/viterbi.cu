@@ -25,20 +25,23 @@ namespace {
 constexpr int kVitThreads = 1024;
 constexpr int kMaxT = 1024;
 
-// reconstruction of state p: r0 (and r1 for V = 2), upstream's recons_state[:, p]
+// reconstruction of state p: r0 (and r1 for V = 2), upstream's recons_state[:, p].  `tl` is the code's table in shared
+// memory: HYB the 512 x 2 fp32 LUT; 1MAD the 1021 possible values (byte sum - 510) / 147.800537109375 (the IEEE quotient
+// upstream computes, tabulated once per CTA instead of divided per evaluation); 3INST needs none.
 template <int CODE>
 __device__ __forceinline__ void recons_of(uint32_t p, const float2 *__restrict__ tl, float &r0, float &r1) {
     if constexpr (CODE == QTIP_CODE_HYB) {
         const uint32_t h = hyb_hash(p);
         const float2 v = tl[(h >> 6) & 511u];
-        r0 = (h & 0x8000u) ? -v.x : v.x;      // quantlut_sym multiplies the first value by -1 when bit 15 of the hash is set
+        // quantlut_sym multiplies the first value by -1 when bit 15 of the hash is set: flip the sign bit
+        r0 = __uint_as_float(__float_as_uint(v.x) ^ ((h << 16) & 0x80000000u));
         r1 = v.y;
     } else if constexpr (CODE == QTIP_CODE_3INST) {
         r0 = __half2float(decode_3inst(p));
         r1 = 0.f;
     } else {
         const uint32_t x = p * 34038481u + 76625530u;
-        r0 = __fdiv_rn((float)((int)__vsadu4(x, 0u) - 510), 147.800537109375f);
+        r0 = reinterpret_cast<const float *>(tl)[__vsadu4(x, 0u)];
         r1 = 0.f;
     }
 }
@@ -90,10 +93,16 @@ __device__ __forceinline__ void viterbi_pass(Smem *sh, float *best0, float *best
             const uint32_t d0 = sub * dchunk;
             float bv = 0.f;
             uint32_t bd = d0;
-            for (uint32_t d = d0; d < d0 + dchunk; d++) {
-                const uint32_t p = g + d * G;
-                const float c = __fadd_rn(err_of<CODE>(p, tl, x0, x1), cur[(g >> KV) + d * Gs]);
-                if (d == d0 || c < bv) { bv = c; bd = d; }
+            // ascending d with a strict "<": the first minimal predecessor wins, as torch.min does
+            uint32_t pcur = g + d0 * G;
+            const float *bcur = cur + (g >> KV) + d0 * Gs;
+            bv = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bcur[0]);
+#pragma unroll 4
+            for (uint32_t d = d0 + 1; d < d0 + dchunk; d++) {
+                pcur += G;
+                bcur += Gs;
+                const float c = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bcur[0]);
+                if (c < bv) { bv = c; bd = d; }
             }
             // combine the sub-ranges of a group (adjacent lanes, ascending d): the lower range wins ties
             for (uint32_t o = 1; o < tpg; o <<= 1) {
@@ -153,7 +162,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     extern __shared__ __align__(16) uint8_t smem_raw[];
     Smem *sh = reinterpret_cast<Smem *>(smem_raw);
     static_assert(sizeof(Smem) % 16 == 0, "what follows the control block needs 8- and 16-byte alignment");
-    float2 *tl = reinterpret_cast<float2 *>(smem_raw + sizeof(Smem));                 // 512 entries (HYB only)
+    float2 *tl = reinterpret_cast<float2 *>(smem_raw + sizeof(Smem));                 // 4 KiB: the code's table (HYB, 1MAD)
     const uint32_t G = 65536u >> KV;
     float *best0 = reinterpret_cast<float *>(smem_raw + sizeof(Smem) + 512 * sizeof(float2));
     float *best1 = best0 + G;
@@ -161,6 +170,9 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     uint8_t *bp = workspace + (size_t)blockIdx.x * S * G;
     if constexpr (CODE == QTIP_CODE_HYB)
         for (int i = threadIdx.x; i < 512; i += kVitThreads) tl[i] = tlut[i];
+    if constexpr (CODE == QTIP_CODE_1MAD)
+        for (int i = threadIdx.x; i < 1024; i += kVitThreads)
+            reinterpret_cast<float *>(tl)[i] = __fdiv_rn((float)(i - 510), 147.800537109375f);
     for (long b = blockIdx.x; b < N; b += gridDim.x) {
         __syncthreads();
         for (int t = threadIdx.x; t < T; t += kVitThreads) sh->x[t] = __half2float(X[b * T + t]);
