@@ -166,3 +166,24 @@ def test_quip_params_validation():
         check_quip_params(dict(ok, skip_list=["0_q"]), shape)
     with pytest.raises(ValueError, match="built for K"):
         check_quip_params(dict(ok, K=3), shape)
+
+
+def test_bench_arms_print_the_same_config():
+    """Both arms of bench.py derive `config` from the same rule: fused q||k||v / gate||up matrices for the 7B shape on one
+    GPU at batch 1, separate matrices everywhere else."""
+    import argparse
+    import importlib.util
+    import os
+    from conftest import ROOT
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    base = dict(separate_qkv=False, workload="llama2-7b", gpus=1, batch=1, prompt=128)
+    ns = argparse.Namespace(**base)
+    os.environ.pop("WORLD_SIZE", None)
+    assert bench.use_fused_matrices(ns)
+    assert "fused_matrices" in bench.workload_config(ns.workload, ns.prompt, 1, bench.use_fused_matrices(ns))
+    for change in (dict(separate_qkv=True), dict(workload="llama3-405b"), dict(gpus=2), dict(batch=8)):
+        assert not bench.use_fused_matrices(argparse.Namespace(**dict(base, **change))), change
+    assert "fused_matrices" not in bench.workload_config("llama3-405b", 256, 8, False)
+    assert bench.algorithmic_bytes(4096, 4096, 2) == 4210688
