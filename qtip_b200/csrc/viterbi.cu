@@ -28,26 +28,29 @@ constexpr int kMaxT = 1024;
 // reconstruction of state p: r0 (and r1 for V = 2), upstream's recons_state[:, p].  `tl` is the code's table in shared
 // memory: HYB the 512 x 2 fp32 LUT; 1MAD the 1021 possible values (byte sum - 510) / 147.800537109375 (the IEEE quotient
 // upstream computes, tabulated once per CTA instead of divided per evaluation); 3INST needs none.
+// (tl: 32-bit shared-memory address of the table - the loops are bound by instruction issue, and 64-bit generic
+// address arithmetic would cost two more instructions per evaluation)
 template <int CODE>
-__device__ __forceinline__ void recons_of(uint32_t p, const float2 *__restrict__ tl, float &r0, float &r1) {
+__device__ __forceinline__ void recons_of(uint32_t p, uint32_t tl, float &r0, float &r1) {
     if constexpr (CODE == QTIP_CODE_HYB) {
         const uint32_t h = hyb_hash(p);
-        const float2 v = tl[(h >> 6) & 511u];
+        float vx, vy;
+        asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(vx), "=f"(vy) : "r"(tl + ((h >> 3) & 0xFF8u)));    // entry (h >> 6) & 511
         // quantlut_sym multiplies the first value by -1 when bit 15 of the hash is set: flip the sign bit
-        r0 = __uint_as_float(__float_as_uint(v.x) ^ ((h << 16) & 0x80000000u));
-        r1 = v.y;
+        r0 = __uint_as_float(__float_as_uint(vx) ^ ((h << 16) & 0x80000000u));
+        r1 = vy;
     } else if constexpr (CODE == QTIP_CODE_3INST) {
         r0 = __half2float(decode_3inst(p));
         r1 = 0.f;
     } else {
         const uint32_t x = p * 34038481u + 76625530u;
-        r0 = reinterpret_cast<const float *>(tl)[__vsadu4(x, 0u)];
+        asm("ld.shared.f32 %0, [%1];" : "=f"(r0) : "r"(tl + __vsadu4(x, 0u) * 4u));
         r1 = 0.f;
     }
 }
 
 template <int CODE>
-__device__ __forceinline__ float err_of(uint32_t p, const float2 *__restrict__ tl, float x0, float x1) {
+__device__ __forceinline__ float err_of(uint32_t p, uint32_t tl, float x0, float x1) {
     float r0, r1;
     recons_of<CODE>(p, tl, r0, r1);
     const float d0 = __fsub_rn(r0, x0);
@@ -69,7 +72,7 @@ struct __align__(16) Smem {    // sizeof is a multiple of 16: the table (8-byte 
 // One pass of upstream's viterbi().  xoff: the pass reads x[(t + xoff) % T] (the rolled sequence of the first pass).
 // Leaves the first minimal final state in sh->arg; back-pointers in bp[i*G + g], i = 1..S-1.
 template <int CODE>
-__device__ __forceinline__ void viterbi_pass(Smem *sh, float *best0, float *best1, const float2 *tl, uint8_t *__restrict__ bp, int T, int KV,
+__device__ __forceinline__ void viterbi_pass(Smem *sh, float *best0, float *best1, uint32_t tl, uint8_t *__restrict__ bp, int T, int KV,
                              int xoff, bool has_overlap, uint32_t overlap, float *final_cost) {
     constexpr int V = CODE == QTIP_CODE_HYB ? 2 : 1;
     const int S = T / V;
@@ -95,13 +98,16 @@ __device__ __forceinline__ void viterbi_pass(Smem *sh, float *best0, float *best
             uint32_t bd = d0;
             // ascending d with a strict "<": the first minimal predecessor wins, as torch.min does
             uint32_t pcur = g + d0 * G;
-            const float *bcur = cur + (g >> KV) + d0 * Gs;
-            bv = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bcur[0]);
+            uint32_t bcur = (uint32_t)__cvta_generic_to_shared(cur) + ((g >> KV) + d0 * Gs) * 4u;
+            float bprev;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(bprev) : "r"(bcur) : "memory");
+            bv = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bprev);
 #pragma unroll 4
             for (uint32_t d = d0 + 1; d < d0 + dchunk; d++) {
                 pcur += G;
-                bcur += Gs;
-                const float c = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bcur[0]);
+                bcur += Gs * 4u;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(bprev) : "r"(bcur) : "memory");
+                const float c = __fadd_rn(err_of<CODE>(pcur, tl, x0, x1), bprev);
                 if (c < bv) { bv = c; bd = d; }
             }
             // combine the sub-ranges of a group (adjacent lanes, ascending d): the lower range wins ties
@@ -173,13 +179,14 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     if constexpr (CODE == QTIP_CODE_1MAD)
         for (int i = threadIdx.x; i < 1024; i += kVitThreads)
             reinterpret_cast<float *>(tl)[i] = __fdiv_rn((float)(i - 510), 147.800537109375f);
+    const uint32_t tl_addr = (uint32_t)__cvta_generic_to_shared(tl);
     for (long b = blockIdx.x; b < N; b += gridDim.x) {
         __syncthreads();
         for (int t = threadIdx.x; t < T; t += kVitThreads) sh->x[t] = __half2float(X[b * T + t]);
         __syncthreads();
         // first pass: the sequence rolled by T/(2V)*V (rolled[t] = x[t - roll]), free ends
         const int roll = T / (2 * V) * V;
-        viterbi_pass<CODE>(sh, best0, best1, tl, bp, T, KV, T - roll, false, 0u, nullptr);
+        viterbi_pass<CODE>(sh, best0, best1, tl_addr, bp, T, KV, T - roll, false, 0u, nullptr);
         // the state at step T/(2V) of the rolled walk is where the original sequence starts
         if (threadIdx.x == 0) {
             uint32_t st = sh->arg;
@@ -192,7 +199,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
         __syncthreads();
         const uint32_t overlap = sh->arg;
         __syncthreads();
-        viterbi_pass<CODE>(sh, best0, best1, tl, bp, T, KV, 0, true, overlap, final_cost ? final_cost + b : nullptr);
+        viterbi_pass<CODE>(sh, best0, best1, tl_addr, bp, T, KV, 0, true, overlap, final_cost ? final_cost + b : nullptr);
         if (threadIdx.x == 0) {
             uint32_t st = sh->arg;
             int *out = states + b * S;
